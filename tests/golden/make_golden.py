@@ -1,0 +1,137 @@
+"""Generate the golden fixtures in this directory from the reference's own
+Python packers (CPU only).
+
+Usage:  python tests/golden/make_golden.py <path-to-reference-checkout>
+
+The reference checkout is only needed to (re)generate the fixtures; the tests
+read the committed ``*.npz`` files and never import the reference.  All inputs
+are seeded, so a rerun reproduces the files byte for byte (up to zip
+metadata).
+
+What is recorded (every array is the reference's output for the stated
+inputs):
+  scalar_types.npz   ids and min/max of uint4b8 / uint4 / uint8b128 / uint8
+  repack_*.npz       gptq_pack / awq_pack inputs, sort indices, and the
+                     expected Marlin layout from marlin_weights(get_weight_perm)
+  perms.npz          marlin_permute_scales (grouped and channel-wise),
+                     marlin_permute_bias, marlin_zero_points,
+                     awq_to_marlin_zero_points
+  gemm_*.npz         marlin_quantize / awq_marlin_quantize outputs (w_ref,
+                     Marlin weights, scales, zero-points, g_idx, sort indices),
+                     an activation matrix and the fp32 product a @ w_ref
+"""
+
+import os
+import sys
+
+import numpy as np
+
+
+def _bits16(t):
+    """torch fp16/bf16 tensor -> uint16 bit pattern."""
+    import torch
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16).copy()
+
+
+def main(ref_root: str) -> None:
+    sys.path.insert(0, ref_root)
+    import torch
+    from vllm.model_executor.layers.quantization.utils import marlin_utils as mu
+    from vllm.model_executor.layers.quantization.utils import marlin_utils_test as mt
+    from vllm.model_executor.layers.quantization.utils import quant_utils as qu
+    from vllm.scalar_type import scalar_types
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    types = {"uint4b8": scalar_types.uint4b8, "uint4": scalar_types.uint4,
+             "uint8b128": scalar_types.uint8b128, "uint8": scalar_types.uint8}
+
+    # ---- scalar types -----------------------------------------------------
+    np.savez(os.path.join(here, "scalar_types.npz"),
+             names=np.array(list(types)),
+             ids=np.array([t.id for t in types.values()], dtype=np.int64),
+             mins=np.array([t.min() for t in types.values()], dtype=np.int64),
+             maxs=np.array([t.max() for t in types.values()], dtype=np.int64),
+             size_bits=np.array([t.size_bits for t in types.values()], dtype=np.int64))
+
+    # ---- repack -----------------------------------------------------------
+    rng = np.random.default_rng(0)
+    for bits in (4, 8):
+        for (K, N) in ((128, 64), (256, 192)):
+            q = torch.from_numpy(rng.integers(0, 1 << bits, size=(K, N), dtype=np.int32))
+            g_idx = torch.from_numpy((np.arange(K) // 32)[rng.permutation(K)].astype(np.int32))
+            gptq_in = qu.gptq_pack(q, bits, K, N)
+            awq_in = qu.awq_pack(q, bits, K, N)
+            wperm = mt.get_weight_perm(bits)
+            expect = mt.marlin_weights(q, K, N, bits, wperm)
+            q_sorted, g_sorted, sort_idx = qu.sort_weights(q, g_idx)
+            expect_perm = mt.marlin_weights(q_sorted, K, N, bits, wperm)
+            np.savez_compressed(
+                os.path.join(here, f"repack_b{bits}_k{K}_n{N}.npz"),
+                q=q.numpy(), gptq_in=gptq_in.numpy(), awq_in=awq_in.numpy(),
+                expect=expect.numpy(), g_idx=g_idx.numpy(),
+                sort_idx=sort_idx.numpy(), g_sorted=g_sorted.numpy(),
+                expect_perm=expect_perm.numpy(),
+                weight_perm=wperm.numpy())
+
+    # ---- scale / zero-point / bias permutations ---------------------------
+    K, N = 512, 256
+    s_grouped = torch.from_numpy(rng.random((K // 128, N), dtype=np.float32)).half()
+    s_channel = torch.from_numpy(rng.random((1, N), dtype=np.float32)).half()
+    bias = torch.from_numpy(rng.standard_normal(N).astype(np.float32)).half()
+    out = dict(
+        s_grouped=s_grouped.numpy(), s_channel=s_channel.numpy(), bias=bias.numpy(),
+        s_grouped_perm=mu.marlin_permute_scales(s_grouped, K, N, 128).numpy(),
+        s_channel_perm=mu.marlin_permute_scales(s_channel, K, N, -1).numpy(),
+        s_channel_perm_gk=mu.marlin_permute_scales(s_channel, K, N, K).numpy(),
+        bias_perm=mu.marlin_permute_bias(bias).numpy())
+    for bits in (4, 8):
+        G = K // 128
+        zp = torch.from_numpy(rng.integers(0, 1 << bits, size=(G, N), dtype=np.int32))
+        awq_zp = qu.awq_pack(zp, bits, G, N)
+        out[f"zp{bits}"] = zp.numpy()
+        out[f"zp{bits}_marlin"] = mu.marlin_zero_points(zp, G, N, bits).numpy()
+        out[f"zp{bits}_awq_in"] = awq_zp.numpy()
+        out[f"zp{bits}_awq_marlin"] = mu.awq_to_marlin_zero_points(awq_zp, G, N, bits).numpy()
+    np.savez_compressed(os.path.join(here, "perms.npz"), **out)
+
+    # ---- quantise + GEMM expected values ----------------------------------
+    torch.manual_seed(0)
+    cases = [
+        # name, type, dtype, group, act_order, M, K, N
+        ("u4b8_g128_f16", "uint4b8", torch.float16, 128, False, 16, 256, 128),
+        ("u4b8_g32_bf16", "uint4b8", torch.bfloat16, 32, False, 5, 128, 64),
+        ("u4b8_gm1_f16", "uint4b8", torch.float16, -1, False, 26, 256, 64),
+        ("u4b8_g64_act_bf16", "uint4b8", torch.bfloat16, 64, True, 9, 256, 128),
+        ("u8b128_gm1_f16", "uint8b128", torch.float16, -1, False, 3, 128, 128),
+        ("u8b128_g128_act_f16", "uint8b128", torch.float16, 128, True, 17, 256, 64),
+        ("u4_g128_f16", "uint4", torch.float16, 128, False, 33, 256, 128),
+        ("u4_g64_bf16", "uint4", torch.bfloat16, 64, False, 1, 128, 192),
+    ]
+    for name, tname, dtype, g, act, M, K, N in cases:
+        t = types[tname]
+        w = torch.randn((K, N), dtype=dtype)
+        a = torch.randn((M, K), dtype=dtype)
+        rec = dict(type_id=np.int64(t.id), size_bits=np.int64(t.size_bits),
+                   group_size=np.int64(g), act_order=np.int64(act),
+                   is_bf16=np.int64(dtype == torch.bfloat16),
+                   M=np.int64(M), K=np.int64(K), N=np.int64(N))
+        if tname in ("uint4", "uint8"):
+            w_ref, mq, ms, mzp = mt.awq_marlin_quantize(w, t, g)
+            rec["marlin_zp"] = mzp.numpy()
+        else:
+            w_ref, mq, ms, g_idx, sort_idx, _ = mt.marlin_quantize(w, t, g, act)
+            rec["g_idx"] = g_idx.numpy().astype(np.int32)
+            rec["sort_idx"] = sort_idx.numpy().astype(np.int32)
+        rec["a_bits"] = _bits16(a)
+        rec["w_ref_bits"] = _bits16(w_ref)
+        rec["marlin_q_w"] = mq.numpy()
+        rec["marlin_s_bits"] = _bits16(ms)
+        rec["out_ref"] = (a.float() @ w_ref.float()).numpy()
+        np.savez_compressed(os.path.join(here, f"gemm_{name}.npz"), **rec)
+    print("golden fixtures written to", here)
+
+
+if __name__ == "__main__":
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    main(sys.argv[1])
