@@ -1,0 +1,126 @@
+/*
+ * b200q — C ABI of the B200 (sm_100a) weight-only quantized linear kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream,
+ * launches asynchronously on that stream, performs no host synchronisation
+ * and returns 0 on success or a negative B200Q_E* status.  After a non-zero
+ * return b200q_last_error() gives a message for the calling thread.
+ *
+ * Each declaration names the interface of the reference project that it
+ * replaces (paths relative to the reference's root).
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define B200Q_OK 0
+#define B200Q_EINVAL (-1)      /* argument failed validation                  */
+#define B200Q_EUNSUPPORTED (-2) /* valid request with no kernel (type, shape)  */
+#define B200Q_ECUDA (-3)       /* a CUDA runtime call or launch failed         */
+#define B200Q_ESCRATCH (-4)    /* scratch / workspace too small                */
+
+/* activation / output element type */
+#define B200Q_F16 0
+#define B200Q_BF16 1
+
+/* flags for b200q_marlin_gemm (mirror the op's trailing booleans) */
+#define B200Q_FLAG_K_FULL 1u
+#define B200Q_FLAG_ATOMIC_ADD 2u
+#define B200Q_FLAG_FP32_REDUCE 4u
+#define B200Q_FLAG_ZP_FLOAT 8u
+
+/* opaque stream handle: a cudaStream_t (CUstream) */
+typedef void* b200q_stream_t;
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* b200q_last_error(void);
+
+/* Library version, encoded major*10000 + minor*100 + patch. */
+int b200q_version(void);
+
+/* Number of SMs of the current device (0 on error).  The reference sizes the
+ * GEMM workspace from this (marlin_utils.py:237-245). */
+int b200q_sm_count(void);
+
+/*
+ * GPTQ checkpoint layout -> Marlin tile layout.
+ * Replaces: gptq_marlin_repack, csrc/quantization/gptq_marlin/gptq_marlin_repack.cu:251-322
+ *           (op schema csrc/torch_bindings.cpp:319-321).
+ *   b_q_weight  int32 [size_k/pf, size_n], value k%pf of a word at bit (k%pf)*bits
+ *   perm        int32 [size_k] row gather (output row k reads input row perm[k]) or NULL
+ *   out         int32 [size_k/16, size_n*16/pf]
+ *   size_k % 16 == 0, size_n % 64 == 0, num_bits in {4, 8}; pf = 32/num_bits.
+ */
+int b200q_gptq_marlin_repack(const uint32_t* b_q_weight, const int32_t* perm,
+                             uint32_t* out, int64_t size_k, int64_t size_n,
+                             int num_bits, b200q_stream_t stream);
+
+/*
+ * AWQ checkpoint layout -> Marlin tile layout.
+ * Replaces: awq_marlin_repack, csrc/quantization/gptq_marlin/awq_marlin_repack.cu:189-248
+ *           (op schema csrc/torch_bindings.cpp:325-327).
+ *   b_q_weight  int32 [size_k, size_n/pf], AWQ interleaved column packing
+ *   out         int32 [size_k/16, size_n*16/pf]
+ */
+int b200q_awq_marlin_repack(const uint32_t* b_q_weight, uint32_t* out,
+                            int64_t size_k, int64_t size_n, int num_bits,
+                            b200q_stream_t stream);
+
+/*
+ * out[m, k] = a[m, perm[k]] for 16-bit elements.
+ * Replaces: permute_cols, csrc/permute_cols.cu:14-88 (op schema
+ *           csrc/torch_bindings.cpp:304-305).
+ *   a    [size_m, size_k] 16-bit, row stride lda elements
+ *   out  [size_m, size_k] contiguous
+ */
+int b200q_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* out,
+                       int64_t size_m, int64_t size_k, b200q_stream_t stream);
+
+/*
+ * Bytes of device scratch b200q_marlin_gemm needs for this problem (split-K
+ * partial sums, and the gathered activations for act-order).  Never fails;
+ * returns an upper bound valid for any workspace_len.
+ * Replaces the in-op allocations of c_tmp / a_tmp,
+ * csrc/quantization/gptq_marlin/gptq_marlin.cu:751-763,798-799.
+ */
+size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n,
+                                       int64_t size_k, int has_act_order);
+
+/*
+ * C[M,N] = A[M,K] * dequant(B) (+ bias): the mixed-precision GEMM.
+ * Replaces: gptq_marlin_gemm, csrc/quantization/gptq_marlin/gptq_marlin.cu:674-959
+ *           (op schema csrc/torch_bindings.cpp:308-315).
+ *   a            [size_m, size_k] fp16/bf16, row stride lda (lda % 8 == 0, 16 B aligned)
+ *   b_q_weight   Marlin layout int32 [size_k/16, size_n*16/pf]
+ *   b_scales     [num_groups, size_n] of a's type, already marlin_permute_scales'd
+ *   b_zeros      int32 [num_groups, size_n/pf] Marlin zero-points, or NULL
+ *   g_idx, perm  int32 [size_k] (sorted group ids / sort permutation), both or neither
+ *   b_bias       [size_n] of a's type, marlin_permute_bias'd, or NULL
+ *   c            [size_m, size_n] contiguous, written
+ *   scratch      >= b200q_marlin_gemm_scratch_bytes(...) bytes, 256 B aligned
+ *   workspace    int32 [workspace_len], all zero on entry, zero again when the
+ *                kernels finish; workspace_len >= 1 (the reference passes #SMs)
+ *   b_q_type_id  ScalarType id (csrc/core/scalar_type.hpp:124-157): uint4b8,
+ *                uint8b128 without zero-points; uint4, uint8 with zero-points
+ *   a_dtype      B200Q_F16 or B200Q_BF16
+ */
+int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q_weight,
+                      const void* b_scales, const uint32_t* b_zeros,
+                      const int32_t* g_idx, const int32_t* perm,
+                      const void* b_bias, void* c, void* scratch,
+                      size_t scratch_bytes, int32_t* workspace,
+                      int64_t workspace_len, int64_t b_q_type_id, int a_dtype,
+                      int64_t size_m, int64_t size_n, int64_t size_k,
+                      int64_t num_groups, unsigned flags, b200q_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,233 @@
+// extern "C" surface of libb200q: argument validation (mirroring the checks of
+// the reference op, csrc/quantization/gptq_marlin/gptq_marlin.cu:688-902), kernel
+// selection and scratch accounting.  No torch types cross this boundary.
+#include <cstring>
+
+#include "common.cuh"
+#include "gemm_stream.cuh"
+
+namespace b200q {
+
+namespace {
+thread_local char g_error[512] = "";
+int g_sm_count[64];
+int g_smem_optin[64];
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+static void query_device(int dev) {
+  int v = 0;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess)
+    g_sm_count[dev & 63] = v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess)
+    g_smem_optin[dev & 63] = v;
+}
+
+int device_sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (g_sm_count[dev & 63] == 0) query_device(dev);
+  return g_sm_count[dev & 63];
+}
+
+int device_max_smem_optin() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (g_smem_optin[dev & 63] == 0) query_device(dev);
+  return g_smem_optin[dev & 63];
+}
+
+int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* out, int64_t size_m,
+                        int64_t size_k, cudaStream_t stream);
+
+namespace {
+
+constexpr int kMaxRowsPerLaunch = 64;
+// upper bound of CTAs any streaming variant launches (2 per SM, <= 256 SMs)
+constexpr int64_t kMaxGrid = 512;
+
+inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+// partial-sum scratch: (grid + slices) slots of (rows x slice width) floats
+int64_t partial_bytes(int64_t size_n) {
+  // a slot holds at most 4096 floats (rows x slice width: 32 x 128 or 64 x 64);
+  // slots are indexed cta + slice < grid + slices <= kMaxGrid + N/64
+  const int64_t nt = size_n / 64;
+  return (kMaxGrid + nt) * 64 * 64 * 4;
+}
+
+}  // namespace
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" const char* b200q_last_error(void) { return g_error; }
+extern "C" int b200q_version(void) { return 100; }
+extern "C" int b200q_sm_count(void) { return device_sm_count(); }
+
+extern "C" size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
+                                                  int has_act_order) {
+  if (size_m <= 0 || size_n <= 0 || size_k <= 0) return 256;
+  int64_t bytes = align_up(partial_bytes(size_n), 256);
+  if (has_act_order) bytes += align_up(size_m * size_k * 2, 256);
+  return (size_t)bytes;
+}
+
+extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q_weight,
+                                 const void* b_scales, const uint32_t* b_zeros,
+                                 const int32_t* g_idx, const int32_t* perm, const void* b_bias,
+                                 void* c, void* scratch, size_t scratch_bytes, int32_t* workspace,
+                                 int64_t workspace_len, int64_t b_q_type_id, int a_dtype,
+                                 int64_t size_m, int64_t size_n, int64_t size_k,
+                                 int64_t num_groups, unsigned flags, b200q_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  // ---- type contract ---------------------------------------------------------------
+  int bits = 0;
+  bool type_has_zp = false;
+  if (b_q_type_id == kTypeU4B8) { bits = 4; }
+  else if (b_q_type_id == kTypeU8B128) { bits = 8; }
+  else if (b_q_type_id == kTypeU4) { bits = 4; type_has_zp = true; }
+  else if (b_q_type_id == kTypeU8) { bits = 8; type_has_zp = true; }
+  else {
+    set_error("b_q_type id %lld is not supported (uint4b8, uint8b128, uint4, uint8)",
+              (long long)b_q_type_id);
+    return B200Q_EUNSUPPORTED;
+  }
+  const bool has_zp = b_zeros != nullptr;
+  B200Q_REQUIRE(!has_zp || type_has_zp, B200Q_EINVAL,
+                "b_q_type must be u4 or u8 when has_zp = True");
+  B200Q_REQUIRE(has_zp || !type_has_zp, B200Q_EINVAL,
+                "b_q_type must be uint4b8 or uint8b128 when has_zp = False");
+  B200Q_REQUIRE(!(flags & B200Q_FLAG_ZP_FLOAT), B200Q_EUNSUPPORTED,
+                "float zero-points (is_zp_float) are not supported");
+  B200Q_REQUIRE(a_dtype == B200Q_F16 || a_dtype == B200Q_BF16, B200Q_EINVAL,
+                "gpt_marlin_gemm only supports bfloat16 and float16");
+  // ---- shapes ------------------------------------------------------------------------
+  B200Q_REQUIRE(size_m >= 0 && size_n >= 0 && size_k >= 0, B200Q_EINVAL, "negative size");
+  B200Q_REQUIRE(size_k % 16 == 0, B200Q_EINVAL, "size_k = %lld is not divisible by tile_size = 16",
+                (long long)size_k);
+  B200Q_REQUIRE(size_n % 64 == 0, B200Q_EINVAL,
+                "size_n = %lld, is not divisible by min_thread_n = 64", (long long)size_n);
+  if (size_m == 0) return B200Q_OK;
+  B200Q_REQUIRE(size_n > 0 && size_k > 0, B200Q_EINVAL, "Invalid MNK = [%lld, %lld, %lld]",
+                (long long)size_m, (long long)size_n, (long long)size_k);
+  B200Q_REQUIRE(size_n < (1ll << 31) && size_k < (1ll << 31) && size_m < (1ll << 31), B200Q_EINVAL,
+                "size too large");
+  B200Q_REQUIRE(a && b_q_weight && b_scales && c && workspace, B200Q_EINVAL,
+                "null tensor pointer");
+  B200Q_REQUIRE(lda >= size_k && lda % 8 == 0, B200Q_EINVAL, "A.stride(0) must divisible by 8");
+  B200Q_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0, B200Q_EINVAL,
+                "A must aligned to 16 bytes");
+  B200Q_REQUIRE((reinterpret_cast<uintptr_t>(c) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(b_q_weight) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(b_scales) & 15) == 0 &&
+                    (!b_zeros || (reinterpret_cast<uintptr_t>(b_zeros) & 15) == 0),
+                B200Q_EINVAL, "tensors must be aligned to 16 bytes");
+  B200Q_REQUIRE(num_groups >= 1, B200Q_EINVAL, "b_scales dim 0 = %lld is not valid",
+                (long long)num_groups);
+  B200Q_REQUIRE((g_idx == nullptr) == (perm == nullptr), B200Q_EINVAL,
+                "g_idx and perm must be given together");
+  const bool has_act_order = g_idx != nullptr;
+  const bool is_k_full = flags & B200Q_FLAG_K_FULL;
+  B200Q_REQUIRE(workspace_len >= 1, B200Q_ESCRATCH, "workspace.numel = %lld is below 1",
+                (long long)workspace_len);
+
+  // ---- group handling (gptq_marlin.cu:765-819) -----------------------------------------
+  int gm;
+  int group_blocks;
+  const int kt_total = (int)(size_k / 16);
+  if (has_act_order) {
+    B200Q_REQUIRE(!has_zp, B200Q_EUNSUPPORTED, "act_order with zero-points is not supported");
+    if (is_k_full) {
+      B200Q_REQUIRE(num_groups > 1, B200Q_EINVAL, "For act_order, num_groups must be > 1");
+      B200Q_REQUIRE(size_k % num_groups == 0, B200Q_EINVAL,
+                    "size_k = %lld, is not divisible by num_groups = %lld", (long long)size_k,
+                    (long long)num_groups);
+      gm = kGrouped;
+    } else {
+      gm = kLookup;
+    }
+  } else if (num_groups > 1) {
+    B200Q_REQUIRE(size_k % num_groups == 0, B200Q_EINVAL,
+                  "size_k = %lld, is not divisible by b_scales.size(0) = %lld", (long long)size_k,
+                  (long long)num_groups);
+    gm = kGrouped;
+  } else {
+    gm = kChannel;
+  }
+  if (gm == kGrouped) {
+    const int64_t group_size = size_k / num_groups;
+    B200Q_REQUIRE(group_size % 16 == 0, B200Q_EUNSUPPORTED,
+                  "group_size = %lld is not a multiple of 16", (long long)group_size);
+    group_blocks = (int)(group_size / 16);
+  } else {
+    group_blocks = kt_total;  // single group: zero-points (if any) load once
+  }
+
+  // ---- scratch -----------------------------------------------------------------------
+  const size_t need = b200q_marlin_gemm_scratch_bytes(size_m, size_n, size_k, has_act_order);
+  B200Q_REQUIRE(scratch && scratch_bytes >= need, B200Q_ESCRATCH,
+                "scratch of %zu bytes is below the required %zu", scratch_bytes, need);
+  B200Q_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 255) == 0, B200Q_EINVAL,
+                "scratch must be aligned to 256 bytes");
+  float* partials = static_cast<float*>(scratch);
+  const void* a_used = a;
+  int64_t lda_used = lda;
+  if (has_act_order) {
+    // gather the activation columns into sorted-row order once
+    // (gptq_marlin.cu:549-564); the GEMM then reads a contiguous matrix
+    void* a_tmp = static_cast<char*>(scratch) + align_up(partial_bytes(size_n), 256);
+    int rc = launch_permute_cols(a, lda, perm, a_tmp, size_m, size_k, stream);
+    if (rc != B200Q_OK) return rc;
+    a_used = a_tmp;
+    lda_used = size_k;
+  }
+
+  // ---- launches: chunks of up to 64 rows ---------------------------------------------
+  const int nt = (int)(size_n / 64);
+  int64_t max_ctas = workspace_len < kMaxGrid ? workspace_len : kMaxGrid;
+  for (int64_t m0 = 0; m0 < size_m; m0 += kMaxRowsPerLaunch) {
+    const int rows = (int)((size_m - m0) < kMaxRowsPerLaunch ? (size_m - m0) : kMaxRowsPerLaunch);
+    int mb = (rows + 15) / 16;
+    if (mb == 3) mb = 4;
+    int ntw = (mb <= 2 && nt % 2 == 0 && gm != kLookup) ? 2 : 1;
+    StreamParams p;
+    p.a = static_cast<const char*>(a_used) + (size_t)m0 * lda_used * 2;
+    p.lda = lda_used;
+    p.b = b_q_weight;
+    p.scales = b_scales;
+    p.zeros = b_zeros;
+    p.g_idx = g_idx;
+    p.bias = b_bias;
+    p.c = static_cast<char*>(c) + (size_t)m0 * size_n * 2;
+    p.partials = partials;
+    p.counters = workspace;
+    p.m = rows;
+    p.n = (int)size_n;
+    p.k = (int)size_k;
+    p.kt_total = kt_total;
+    p.slices = nt / ntw;
+    p.group_blocks = group_blocks;
+    p.num_groups = (int)num_groups;
+    int rc;
+    if (a_dtype == B200Q_F16) {
+      rc = bits == 4 ? dispatch_stream<half, 4>(p, has_zp, gm, mb, ntw, (int)max_ctas, stream)
+                     : dispatch_stream<half, 8>(p, has_zp, gm, mb, ntw, (int)max_ctas, stream);
+    } else {
+      rc = bits == 4
+               ? dispatch_stream<__nv_bfloat16, 4>(p, has_zp, gm, mb, ntw, (int)max_ctas, stream)
+               : dispatch_stream<__nv_bfloat16, 8>(p, has_zp, gm, mb, ntw, (int)max_ctas, stream);
+    }
+    if (rc == B200Q_EUNSUPPORTED && g_error[0] == 0)
+      set_error("Unsupported shapes: MNK = [%lld, %lld, %lld]", (long long)size_m,
+                (long long)size_n, (long long)size_k);
+    if (rc != B200Q_OK) return rc;
+  }
+  return B200Q_OK;
+}

@@ -1,0 +1,260 @@
+// Shared device/host helpers for the b200q kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/b200q.h"
+
+namespace b200q {
+
+// ---- host-side error reporting ---------------------------------------------
+void set_error(const char* fmt, ...);
+
+#define B200Q_REQUIRE(cond, code, ...)  \
+  do {                                  \
+    if (!(cond)) {                      \
+      ::b200q::set_error(__VA_ARGS__);  \
+      return (code);                    \
+    }                                   \
+  } while (0)
+
+#define B200Q_CUDA_OK(expr)                                                      \
+  do {                                                                           \
+    cudaError_t e__ = (expr);                                                    \
+    if (e__ != cudaSuccess) {                                                    \
+      ::b200q::set_error("%s failed: %s", #expr, cudaGetErrorString(e__));       \
+      return B200Q_ECUDA;                                                        \
+    }                                                                            \
+  } while (0)
+
+// ScalarType ids (exponent | mantissa<<8 | signed<<16 | bias<<17 | ...).
+constexpr int64_t kTypeU4B8 = 4ll << 8 | 8ll << 17 | 1ll << 50;
+constexpr int64_t kTypeU4 = 4ll << 8 | 1ll << 50;
+constexpr int64_t kTypeU8B128 = 8ll << 8 | 128ll << 17 | 1ll << 50;
+constexpr int64_t kTypeU8 = 8ll << 8 | 1ll << 50;
+
+int device_sm_count();
+int device_max_smem_optin();
+
+// ---- device helpers ----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// 16-byte async copy global -> shared, L2 only; src_bytes in {0, 16}: 0 zero-fills.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes = 16) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
+               "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// D(16x8,f32) += A(16x16) * B(16x8), 16-bit operands.
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4],
+                                                        uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// ---- packed 16-bit pair arithmetic on raw uint32 ------------------------------
+template <typename T>
+struct Pair;
+template <>
+struct Pair<half> {
+  static __device__ __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+    half2 r = __hsub2(*reinterpret_cast<half2*>(&a), *reinterpret_cast<half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    half2 r = __hmul2(*reinterpret_cast<half2*>(&a), *reinterpret_cast<half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+    half2 r = __hfma2(*reinterpret_cast<half2*>(&a), *reinterpret_cast<half2*>(&b),
+                      *reinterpret_cast<half2*>(&c));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ float to_float(uint16_t v) {
+    return __half2float(__ushort_as_half(v));
+  }
+  static __device__ __forceinline__ uint16_t from_float(float f) {
+    return __half_as_ushort(__float2half_rn(f));
+  }
+};
+template <>
+struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t sub(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r =
+        __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r =
+        __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  static __device__ __forceinline__ float to_float(uint16_t v) {
+    return __uint_as_float(static_cast<uint32_t>(v) << 16);
+  }
+  static __device__ __forceinline__ uint16_t from_float(float f) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+  }
+};
+
+// Duplicate the low / high 16 bits of x into both halves.
+__device__ __forceinline__ uint32_t dup_lo(uint32_t x) { return __byte_perm(x, x, 0x1010); }
+__device__ __forceinline__ uint32_t dup_hi(uint32_t x) { return __byte_perm(x, x, 0x3232); }
+
+// ---- integer code -> 16-bit float pairs (exact) --------------------------------
+// One 32-bit word of the Marlin layout expands to pairs (k, k+1) for the two
+// 8-column blocks of a 16-column sub-tile:
+//   4-bit: out[0] = rows {2q,2q+1} block 0, out[1] = rows {2q+8,2q+9} block 0,
+//          out[2], out[3] the same for block 1.
+//   8-bit: out[0] = rows {2q,2q+1}, out[1] = rows {2q+8,2q+9} of ONE block.
+// BIASED selects the built-in offset (8 / 128); otherwise the raw code value is
+// produced (zero-point types, and the zero-points themselves).
+// Integers up to 2^11 (fp16) / 2^8 (bf16) are exact in the target type, so the
+// "or into the mantissa of 1024.0 / 128.0, then subtract" conversion is exact.
+template <typename T, bool BIASED>
+__device__ __forceinline__ void dequant4(uint32_t q, uint32_t (&out)[4]);
+
+template <>
+__device__ __forceinline__ void dequant4<half, true>(uint32_t q, uint32_t (&out)[4]) {
+  const uint32_t EX = 0x64006400u;   // 1024.0
+  const uint32_t SUB = 0x64086408u;  // 1032.0
+  const uint32_t MUL = 0x2c002c00u;  // 1/16
+  const uint32_t ADD = 0xd480d480u;  // -72.0
+  out[0] = Pair<half>::sub((q & 0x000f000fu) | EX, SUB);
+  out[1] = Pair<half>::fma((q & 0x00f000f0u) | EX, MUL, ADD);
+  q >>= 8;
+  out[2] = Pair<half>::sub((q & 0x000f000fu) | EX, SUB);
+  out[3] = Pair<half>::fma((q & 0x00f000f0u) | EX, MUL, ADD);
+}
+template <>
+__device__ __forceinline__ void dequant4<half, false>(uint32_t q, uint32_t (&out)[4]) {
+  const uint32_t EX = 0x64006400u;
+  const uint32_t MUL = 0x2c002c00u;
+  const uint32_t ADD = 0xd400d400u;  // -64.0
+  out[0] = Pair<half>::sub((q & 0x000f000fu) | EX, EX);
+  out[1] = Pair<half>::fma((q & 0x00f000f0u) | EX, MUL, ADD);
+  q >>= 8;
+  out[2] = Pair<half>::sub((q & 0x000f000fu) | EX, EX);
+  out[3] = Pair<half>::fma((q & 0x00f000f0u) | EX, MUL, ADD);
+}
+template <>
+__device__ __forceinline__ void dequant4<__nv_bfloat16, true>(uint32_t q, uint32_t (&out)[4]) {
+  const uint32_t EX = 0x43004300u;   // 128.0
+  const uint32_t SUB = 0x43084308u;  // 136.0
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[i] = Pair<__nv_bfloat16>::sub((q & 0x000f000fu) | EX, SUB);
+    q >>= 4;
+  }
+}
+template <>
+__device__ __forceinline__ void dequant4<__nv_bfloat16, false>(uint32_t q, uint32_t (&out)[4]) {
+  const uint32_t EX = 0x43004300u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[i] = Pair<__nv_bfloat16>::sub((q & 0x000f000fu) | EX, EX);
+    q >>= 4;
+  }
+}
+
+template <typename T, bool BIASED>
+__device__ __forceinline__ void dequant8(uint32_t q, uint32_t (&out)[2]);
+
+template <>
+__device__ __forceinline__ void dequant8<half, true>(uint32_t q, uint32_t (&out)[2]) {
+  const uint32_t SUB = 0x64806480u;  // 1152.0
+  out[0] = Pair<half>::sub(__byte_perm(q, 0x64646464u, 0x4240), SUB);
+  out[1] = Pair<half>::sub(__byte_perm(q, 0x64646464u, 0x4341), SUB);
+}
+template <>
+__device__ __forceinline__ void dequant8<half, false>(uint32_t q, uint32_t (&out)[2]) {
+  const uint32_t SUB = 0x64006400u;
+  out[0] = Pair<half>::sub(__byte_perm(q, 0x64646464u, 0x4240), SUB);
+  out[1] = Pair<half>::sub(__byte_perm(q, 0x64646464u, 0x4341), SUB);
+}
+template <bool BIASED>
+__device__ __forceinline__ void dequant8_bf16(uint32_t q, uint32_t (&out)[2]) {
+  // 8-bit codes do not fit bf16's 7 mantissa bits: go through fp32
+  // (2^23 + code) and convert the exact small integer back.
+  const float off = BIASED ? 8388736.0f : 8388608.0f;
+  float f0 = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7440)) - off;
+  float f1 = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7441)) - off;
+  float f2 = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7442)) - off;
+  float f3 = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7443)) - off;
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(f0, f2);
+  __nv_bfloat162 p1 = __floats2bfloat162_rn(f1, f3);
+  out[0] = *reinterpret_cast<uint32_t*>(&p0);
+  out[1] = *reinterpret_cast<uint32_t*>(&p1);
+}
+template <>
+__device__ __forceinline__ void dequant8<__nv_bfloat16, true>(uint32_t q, uint32_t (&out)[2]) {
+  dequant8_bf16<true>(q, out);
+}
+template <>
+__device__ __forceinline__ void dequant8<__nv_bfloat16, false>(uint32_t q, uint32_t (&out)[2]) {
+  dequant8_bf16<false>(q, out);
+}
+
+// Position of output column n inside the 32-column "single" permutation used
+// for channel-wise scales and bias: stored position 8*i + jj of a chunk holds
+// column 2*i + [0,1,8,9,16,17,24,25][jj].
+__host__ __device__ __forceinline__ int single_perm_pos(int n) {
+  int r = n & 31;
+  return (n & ~31) + 8 * ((r & 7) >> 1) + 2 * (r >> 3) + (r & 1);
+}
+// Position of column n inside the 64-column grouped-scale permutation: stored
+// position 8*i + j holds column i + 8*j.
+__host__ __device__ __forceinline__ int grouped_perm_pos(int n) {
+  int r = n & 63;
+  return (n & ~63) + 8 * (r & 7) + (r >> 3);
+}
+
+}  // namespace b200q

@@ -1,0 +1,77 @@
+"""Sub-byte scalar type descriptors with the reference's 64-bit id encoding
+(vllm/scalar_type.py:23-164, csrc/core/scalar_type.hpp:17-157).  Only the
+integer weight types of the quantized linear path are tabulated."""
+from __future__ import annotations
+
+import functools
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class ScalarType:
+    exponent: int
+    mantissa: int
+    signed: bool
+    bias: int
+    _finite_values_only: bool = False
+    nan_repr: int = 1  # IEEE_754; meaningless for integer types
+
+    @functools.cached_property
+    def id(self) -> int:
+        val, off = 0, 0
+        for member, width in ((self.exponent, 8), (self.mantissa, 8), (int(self.signed), 1),
+                              (self.bias, 32), (int(self._finite_values_only), 1),
+                              (self.nan_repr, 8)):
+            val |= (int(member) & ((1 << width) - 1)) << off
+            off += width
+        return val
+
+    @property
+    def size_bits(self) -> int:
+        return self.exponent + self.mantissa + int(self.signed)
+
+    def is_integer(self) -> bool:
+        return self.exponent == 0
+
+    def is_floating_point(self) -> bool:
+        return self.exponent != 0
+
+    def is_signed(self) -> bool:
+        return self.signed
+
+    def has_bias(self) -> bool:
+        return self.bias != 0
+
+    def min(self) -> int:
+        assert self.is_integer()
+        raw = -(1 << (self.size_bits - 1)) if self.signed else 0
+        return raw - self.bias
+
+    def max(self) -> int:
+        assert self.is_integer()
+        return (1 << self.mantissa) - 1 - self.bias
+
+    @classmethod
+    def uint(cls, size_bits: int, bias: int | None) -> "ScalarType":
+        return cls(0, size_bits, False, bias or 0)
+
+    @classmethod
+    def from_id(cls, type_id: int) -> "ScalarType":
+        for t in _ALL:
+            if t.id == type_id:
+                return t
+        raise ValueError(f"unknown ScalarType id {type_id}")
+
+    def __str__(self) -> str:
+        s = f"uint{self.size_bits}" if not self.signed else f"int{self.size_bits}"
+        return s + (f"b{self.bias}" if self.bias else "")
+
+
+class scalar_types:
+    uint4 = ScalarType.uint(4, None)
+    uint8 = ScalarType.uint(8, None)
+    uint4b8 = ScalarType.uint(4, 8)
+    uint8b128 = ScalarType.uint(8, 128)
+
+
+_ALL = (scalar_types.uint4, scalar_types.uint8, scalar_types.uint4b8, scalar_types.uint8b128)
