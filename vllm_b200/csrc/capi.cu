@@ -1,10 +1,11 @@
 // extern "C" surface of libb200q: argument validation (mirroring the checks of
 // the reference op, csrc/quantization/gptq_marlin/gptq_marlin.cu:688-902), kernel
 // selection and scratch accounting.  No torch types cross this boundary.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
-#include "gemm_stream.cuh"
+#include "gemm_params.cuh"
 
 namespace b200q {
 
@@ -43,6 +44,10 @@ int device_max_smem_optin() {
   return g_smem_optin[dev & 63];
 }
 
+template <typename T, int BITS>
+int dispatch_stream(const StreamParams& p, bool has_zp, int gm, int mb, int ntw, int max_ctas,
+                    cudaStream_t stream);
+
 int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* out, int64_t size_m,
                         int64_t size_k, cudaStream_t stream);
 
@@ -51,6 +56,17 @@ namespace {
 constexpr int kMaxRowsPerLaunch = 64;
 // upper bound of CTAs any streaming variant launches (2 per SM, <= 256 SMs)
 constexpr int64_t kMaxGrid = 512;
+
+// B200Q_STREAM_NTW=1|2 overrides the slice width of the grouped decode kernel
+// at 16 rows or fewer (a tuning knob; both settings give identical results).
+int grouped_ntw() {
+  static int v = 0;
+  if (v == 0) {
+    const char* e = getenv("B200Q_STREAM_NTW");
+    v = (e && e[0] == '1') ? 1 : 2;
+  }
+  return v;
+}
 
 inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
@@ -194,9 +210,14 @@ extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q
   int64_t max_ctas = workspace_len < kMaxGrid ? workspace_len : kMaxGrid;
   for (int64_t m0 = 0; m0 < size_m; m0 += kMaxRowsPerLaunch) {
     const int rows = (int)((size_m - m0) < kMaxRowsPerLaunch ? (size_m - m0) : kMaxRowsPerLaunch);
-    int mb = (rows + 15) / 16;
-    if (mb == 3) mb = 4;
-    int ntw = (mb <= 2 && nt % 2 == 0 && gm != kLookup) ? 2 : 1;
+    // 8-row blocks of A handled per launch: 1, 2, 4 or 8
+    int mb = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
+    // slice width in 64-column tiles: two where the accumulators fit in registers
+    int ntw = 1;
+    if (nt % 2 == 0) {
+      if (gm == kChannel && mb <= 4) ntw = 2;
+      if (gm == kGrouped && mb <= 2) ntw = grouped_ntw();
+    }
     StreamParams p;
     p.a = static_cast<const char*>(a_used) + (size_t)m0 * lda_used * 2;
     p.lda = lda_used;

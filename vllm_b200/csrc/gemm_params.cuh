@@ -1,0 +1,37 @@
+// Parameter block and constants shared by the decode-regime GEMM kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200q {
+
+enum GroupMode : int {
+  kChannel = 0,  // one scale per column, applied in fp32 in the epilogue
+  kGrouped = 1,  // scale group = k / group_size
+  kLookup = 2,   // scale group = g_idx[k] (act-order with a partial K range)
+};
+
+struct StreamParams {
+  const void* a;           // [M, K] 16-bit, row stride lda
+  int64_t lda;
+  const uint32_t* b;       // Marlin layout
+  const void* scales;      // [G, N] 16-bit, permuted
+  const uint32_t* zeros;   // [G, N/pf] or null
+  const int32_t* g_idx;    // [K] or null
+  const void* bias;        // [N] permuted or null
+  void* c;                 // [M, N]
+  float* partials;         // scratch for split slices
+  int32_t* counters;       // zero on entry / exit
+  int m, n, k;
+  int kt_total;            // K / 16
+  int slices;              // N / (64 * NTW)
+  int group_blocks;        // k-tiles per scale group (kGrouped)
+  int num_groups;
+  // weight-embedding constants of the streaming kernel (filled by its launcher)
+  uint32_t c_ex, c_mask_lo, c_mask_hi;
+};
+
+constexpr int kStreamWarps = 8;
+constexpr int kStreamThreads = kStreamWarps * 32;
+
+}  // namespace b200q

@@ -1,10 +1,31 @@
-// Streaming mixed-precision GEMM for the decode regime (up to 64 rows of A per
-// launch): C[M,N] = A[M,K] * dequant(B).
+// Streaming mixed-precision GEMM for the decode regime (up to 32 rows of A per
+// launch): C[M,N] = A[M,K] * dequant(B), grouped or channel-wise scales.
 //
-// The kernel is HBM-bound by design: the packed weights are read exactly once,
-// in 512 B (4-bit) / 1 KB (8-bit) tiles that are contiguous in the Marlin
-// layout, through a deep per-warp cp.async ring, dequantised in registers and
-// fed to mma.sync.m16n8k16 with fp32 accumulation.
+// The kernel is meant to be HBM-bound: the packed weights are read exactly
+// once, in 512 B (4-bit) / 1 KB (8-bit) tiles that are contiguous in the Marlin
+// layout, through a deep per-warp cp.async ring, and fed to mma.sync.m16n8k16
+// with fp32 accumulation.  What limits a streaming kernel of this kind is the
+// instruction count per byte, so the arithmetic is arranged to need almost no
+// ALU work per weight:
+//
+//  * Weights are the 16-row operand of the MMA (C^T = W^T A^T): one MMA covers
+//    a 16(N) x 16(K) sub-tile of weights and 8 rows of A, and the four 16-bit
+//    pairs that one 32-bit word of the Marlin layout expands to are exactly the
+//    four operand registers of that MMA.
+//  * No subtract, no scale multiply before the MMA.  A 4-bit code w is OR-ed
+//    into the mantissa of a 16-bit constant, giving x = OFF + U*w exactly
+//    (fp16: 1024 + w and 1024 + 16 w; bf16: 128 + w and 128 + 8 w, the second
+//    form for codes that sit 4 bits higher in the word): one LOP3 per pair of
+//    weights.  The k-rows of A that meet the U-scaled codes are pre-multiplied
+//    by 1/U (exact power of two).  The MMA then yields
+//    T = sum_k a_k (w_k + OFF_k/U_k).
+//  * The offset term is itself a product with A, so one extra MMA per k-tile
+//    against a constant weight fragment gives corr = sum_k a_k (OFF_k/U_k + bias)
+//    and T - corr = sum_k a_k (w_k - bias) up to fp32 rounding.  A second
+//    constant MMA gives the plain row sums needed for zero-points.
+//  * Group scales are applied to the fp32 group sum (T - corr) when the group
+//    ends, not to every weight: acc += s[n] * (T - corr - z[n] * rowsum).
+//    This is also more accurate than rounding w*s to 16 bits first.
 //
 // Work decomposition.  The weight matrix is cut into column "slices" of NTW
 // 64-column tiles; a slice has KT = K/16 k-tiles, so there are S*KT units of
@@ -18,80 +39,190 @@
 // returned to zero.
 #pragma once
 
-#include "common.cuh"
+#include "gemm_params.cuh"
 
 namespace b200q {
 
-enum GroupMode : int {
-  kChannel = 0,  // one scale per column, applied in fp32 in the epilogue
-  kGrouped = 1,  // scale group = k / group_size
-  kLookup = 2,   // scale group = g_idx[k] (act-order with a partial K range)
+// How weight codes become MMA operands for (element type, weight bits).
+// kEx / kMaskLo / kMaskHi reach the kernel through StreamParams so that they
+// live in registers and every and-or is a single three-register LOP3.
+template <typename T, int BITS>
+struct Emb;
+
+template <>
+struct Emb<half, 4> {
+  static constexpr bool kEmbed = true, kPrescale = true;
+  static constexpr uint32_t kEx = 0x64006400u, kMaskLo = 0x000f000fu, kMaskHi = 0x00f000f0u;
+  static constexpr int kShiftHi = 0;
+  static constexpr uint32_t kAScaleHi = 0x2c002c00u;  // 1/16
+  // offsets as seen by the (prescaled) A rows: lo rows 1024 + bias, hi rows 16 * (64 + bias)
+  static constexpr uint32_t kOffLoBiased = 0x64086408u, kOffHiBiased = 0x64806480u;  // 1032, 1152
+  static constexpr uint32_t kOffLoRaw = 0x64006400u, kOffHiRaw = 0x64006400u;        // 1024, 1024
+  static constexpr uint32_t kOneLo = 0x3c003c00u, kOneHi = 0x4c004c00u;              // 1, 16
+};
+template <>
+struct Emb<__nv_bfloat16, 4> {
+  static constexpr bool kEmbed = true, kPrescale = true;
+  static constexpr uint32_t kEx = 0x43004300u, kMaskLo = 0x000f000fu, kMaskHi = 0x00780078u;
+  static constexpr int kShiftHi = 1;
+  static constexpr uint32_t kAScaleHi = 0x3e003e00u;  // 1/8
+  // lo rows 128 + bias, hi rows 8 * (16 + bias)
+  static constexpr uint32_t kOffLoBiased = 0x43084308u, kOffHiBiased = 0x43404340u;  // 136, 192
+  static constexpr uint32_t kOffLoRaw = 0x43004300u, kOffHiRaw = 0x43004300u;        // 128, 128
+  static constexpr uint32_t kOneLo = 0x3f803f80u, kOneHi = 0x41004100u;              // 1, 8
+};
+template <>
+struct Emb<half, 8> {
+  static constexpr bool kEmbed = true, kPrescale = false;
+  static constexpr uint32_t kEx = 0x64646464u, kMaskLo = 0, kMaskHi = 0;
+  static constexpr int kShiftHi = 0;
+  static constexpr uint32_t kAScaleHi = 0;
+  static constexpr uint32_t kOffLoBiased = 0x64806480u, kOffHiBiased = 0x64806480u;  // 1152
+  static constexpr uint32_t kOffLoRaw = 0x64006400u, kOffHiRaw = 0x64006400u;        // 1024
+  static constexpr uint32_t kOneLo = 0x3c003c00u, kOneHi = 0x3c003c00u;
+};
+template <>
+struct Emb<__nv_bfloat16, 8> {
+  // 8-bit codes do not fit bf16's mantissa: convert exactly through fp32 instead
+  static constexpr bool kEmbed = false, kPrescale = false;
+  static constexpr uint32_t kEx = 0, kMaskLo = 0, kMaskHi = 0;
+  static constexpr int kShiftHi = 0;
+  static constexpr uint32_t kAScaleHi = 0;
+  static constexpr uint32_t kOffLoBiased = 0, kOffHiBiased = 0, kOffLoRaw = 0, kOffHiRaw = 0;
+  static constexpr uint32_t kOneLo = 0x3f803f80u, kOneHi = 0x3f803f80u;
 };
 
-struct StreamParams {
-  const void* a;           // [M, K] 16-bit, row stride lda
-  int64_t lda;
-  const uint32_t* b;       // Marlin layout
-  const void* scales;      // [G, N] 16-bit, permuted
-  const uint32_t* zeros;   // [G, N/pf] or null
-  const int32_t* g_idx;    // [K] or null
-  const void* bias;        // [N] permuted or null
-  void* c;                 // [M, N]
-  float* partials;         // scratch for split slices
-  int32_t* counters;       // zero on entry / exit
-  int m, n, k;
-  int kt_total;            // K / 16
-  int slices;              // N / (64 * NTW)
-  int group_blocks;        // k-tiles per scale group (kGrouped)
-  int num_groups;
-};
+// (a & b) | c in one instruction, all operands in registers
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
 
-constexpr int kStreamWarps = 8;
-constexpr int kStreamThreads = kStreamWarps * 32;
+// The four operand registers of the weight side of one MMA (16 columns x 16
+// k-rows): {cols 0-7 k 0-7, cols 8-15 k 0-7, cols 0-7 k 8-15, cols 8-15 k 8-15}.
+template <typename T, int BITS, bool BIASED>
+__device__ __forceinline__ void expand(const uint32_t* w, int sub, uint32_t ex, uint32_t mlo,
+                                       uint32_t mhi, uint32_t (&f)[4]) {
+  using E = Emb<T, BITS>;
+  if constexpr (BITS == 4) {
+    const uint32_t q = w[sub];
+    f[0] = and_or(q, mlo, ex);
+    f[1] = and_or(q >> 8, mlo, ex);
+    f[2] = and_or(q >> E::kShiftHi, mhi, ex);
+    f[3] = and_or(q >> (8 + E::kShiftHi), mhi, ex);
+  } else if constexpr (E::kEmbed) {
+    f[0] = __byte_perm(w[2 * sub], ex, 0x4240);
+    f[1] = __byte_perm(w[2 * sub + 1], ex, 0x4240);
+    f[2] = __byte_perm(w[2 * sub], ex, 0x4341);
+    f[3] = __byte_perm(w[2 * sub + 1], ex, 0x4341);
+  } else {
+    uint32_t t0[2], t1[2];
+    dequant8<T, BIASED>(w[2 * sub], t0);
+    dequant8<T, BIASED>(w[2 * sub + 1], t1);
+    f[0] = t0[0]; f[1] = t1[0]; f[2] = t0[1]; f[3] = t1[1];
+  }
+}
 
-template <int BITS, bool HAS_ZP, int GM, int MB, int NTW>
+template <typename T>
+__device__ __forceinline__ float lo16_to_float(uint32_t x);
+template <typename T>
+__device__ __forceinline__ float hi16_to_float(uint32_t x);
+template <>
+__device__ __forceinline__ float lo16_to_float<half>(uint32_t x) {
+  return __half2float(__ushort_as_half((uint16_t)(x & 0xffffu)));
+}
+template <>
+__device__ __forceinline__ float hi16_to_float<half>(uint32_t x) {
+  return __half2float(__ushort_as_half((uint16_t)(x >> 16)));
+}
+template <>
+__device__ __forceinline__ float lo16_to_float<__nv_bfloat16>(uint32_t x) {
+  return __uint_as_float(x << 16);
+}
+template <>
+__device__ __forceinline__ float hi16_to_float<__nv_bfloat16>(uint32_t x) {
+  return __uint_as_float(x & 0xffff0000u);
+}
+
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
+               : "=r"(r0), "=r"(r1)
+               : "r"(addr));
+}
+
+// MT = number of 8-row blocks of A (1, 2, 4); NTW = 64-column tiles per slice.
+template <int BITS, bool HAS_ZP, int GM, int MT, int NTW>
 struct StreamCfg {
-  static constexpr int kTileBytes = 16 * 64 * BITS / 8;                  // one weight tile
-  static constexpr int kWOff = 0;
-  static constexpr int kAOff = kWOff + NTW * kTileBytes;                 // MB x 512 B
-  static constexpr int kSOff = kAOff + MB * 512;                         // NTW x 128 B scales
-  static constexpr int kZOff = kSOff + (GM == kGrouped ? NTW * 128 : 0); // NTW x (32|64) B zeros
-  static constexpr int kZBytes = HAS_ZP ? NTW * 8 * BITS : 0;
-  static constexpr int kStageBytes = (kZOff + kZBytes + 127) / 128 * 128;
-  // ring depth: as deep as ~96 KB of shared memory per CTA allows, 3..8 stages
-  static constexpr int kDepthFit = 96 * 1024 / (kStageBytes * kStreamWarps);
+  static constexpr int kTileBytes = 16 * 64 * BITS / 8;  // one weight tile
+  static constexpr int kAOff = NTW * kTileBytes;         // A rows (32 B each) after the weights
+  static constexpr int kABytes = MT * 256;
+  static constexpr int kStageBytes = kAOff + kABytes;
+  // per-warp group slots (scales, zero-points), used in rotation; more slots than
+  // ring stages, so a slot is never refilled while its group is still open
+  static constexpr int kSlots = 8;
+  static constexpr int kSlotZOff = NTW * 128;
+  static constexpr int kSlotBytes =
+      (GM == kGrouped) ? (kSlotZOff + (HAS_ZP ? NTW * 8 * BITS : 0)) : 0;
+  static constexpr int kGroupBytes = kSlots * kSlotBytes;
+  // ring depth: as deep as ~88 KB of shared memory per CTA allows, 3..8 stages
+  static constexpr int kDepthFit = (88 * 1024 / kStreamWarps - kGroupBytes) / kStageBytes;
   static constexpr int kDepth = kDepthFit > 8 ? 8 : (kDepthFit < 3 ? 3 : kDepthFit);
-  static constexpr int kRingBytes = kStageBytes * kDepth * kStreamWarps;
-  // reduction buffer: one 16-row block of every warp's accumulators
-  static constexpr int kRedStride = 64 * NTW + 8;  // floats; +8 keeps float2 stores conflict-free
-  static constexpr int kRedBytes = kStreamWarps * 16 * kRedStride * 4;
+  static constexpr int kWarpBytes = kStageBytes * kDepth + kGroupBytes;
+  static constexpr int kRingBytes = kWarpBytes * kStreamWarps;
+  // reduction buffer: one 8-row block of every warp's accumulators, [row][column]
+  static constexpr int kRedStride = 64 * NTW + 4;  // floats; +4 keeps the scalar stores conflict-free
+  static constexpr int kRedBytes = kStreamWarps * 8 * kRedStride * 4;
   static constexpr int kSmemBytes = kRingBytes > kRedBytes ? kRingBytes : kRedBytes;
-  static constexpr int kEpt = 4 * NTW;  // output elements per thread per 16-row block
-  static constexpr int kSlotFloats = MB * 16 * 64 * NTW;
+  static constexpr int kEpt = 2 * NTW;  // output elements per thread per 8-row block
+  static constexpr int kSlotFloats = MT * 8 * 64 * NTW;
 };
 
-template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, int MINB>
+template <typename T, int BITS, bool HAS_ZP, int GM, int MT, int NTW, int MINB>
 __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const StreamParams p) {
-  using Cfg = StreamCfg<BITS, HAS_ZP, GM, MB, NTW>;
+  using Cfg = StreamCfg<BITS, HAS_ZP, GM, MT, NTW>;
+  using E = Emb<T, BITS>;
+  static_assert(GM == kChannel || GM == kGrouped, "lookup mode runs gemm_lookup_kernel");
   constexpr int D = Cfg::kDepth;
-  static_assert(D >= 2, "ring too shallow");
+  constexpr bool kBiased = !HAS_ZP;
+  constexpr int kWordsPerTile = BITS == 4 ? 4 : 8;  // words per lane per tile
   extern __shared__ __align__(128) unsigned char smem[];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int c8 = lane >> 2;  // column inside an 8-wide block
+  const int q = lane & 3;
+  const int c8 = lane >> 2;
   const int KT = p.kt_total;
   const int NT = p.n / 64;
-  const uint16_t* __restrict__ A = static_cast<const uint16_t*>(p.a);
   const uint16_t* __restrict__ S = static_cast<const uint16_t*>(p.scales);
+  const uint32_t ex = p.c_ex, mlo = p.c_mask_lo, mhi = p.c_mask_hi;
 
   const long long total = (long long)p.slices * KT;
   const long long u_begin = total * blockIdx.x / gridDim.x;
   const long long u_end = total * (blockIdx.x + 1) / gridDim.x;
 
-  const uint32_t ring = smem_u32(smem) + warp * (D * Cfg::kStageBytes);
+  const uint32_t ring = smem_u32(smem) + warp * Cfg::kWarpBytes;
+  const uint32_t slots = ring + D * Cfg::kStageBytes;
   float* red = reinterpret_cast<float*>(smem);
   __shared__ int s_is_last;
+
+  // ---- lane-constant addressing of the A rows inside a stage -------------------------
+  // A is staged as rows of 32 B (16 k-values); 16 B chunk (row r, half h) lives at
+  // chunk position 2r + (h ^ ((r >> 2) & 1)) so that ldmatrix reads are conflict-free.
+  // fill: lane copies (row lane/2, half lane%2) of every 16-row block (8 rows when MT == 1:
+  // the upper lanes repeat the lower ones instead of diverging)
+  const int fr = (MT == 1) ? ((lane >> 1) & 7) : (lane >> 1), fh = lane & 1;
+  const uint32_t a_fill_off = (2 * fr + (fh ^ ((fr >> 2) & 1))) * 16;
+  // load: matrix mi = lane/8 -> (8-row block mi/2, half mi%2), row lane%8
+  const int lmi = (MT == 1) ? ((lane >> 3) & 1) : (lane >> 3);
+  const int lr = (lane & 7) + 8 * (lmi >> 1), lh = lmi & 1;
+  const uint32_t a_ld_off = (2 * lr + (lh ^ ((lr >> 2) & 1))) * 16;
+  const size_t w_kt_stride = (size_t)NT * Cfg::kTileBytes;  // bytes between k-tiles
+  constexpr int kABlocks = (MT + 1) / 2;                    // 16-row blocks of A
+  const size_t a_blk_stride = (size_t)16 * p.lda * 2;
+  int a_bytes[kABlocks];
+#pragma unroll
+  for (int i = 0; i < kABlocks; ++i) a_bytes[i] = (i * 16 + fr < p.m) ? 16 : 0;
 
   for (long long u = u_begin; u < u_end;) {
     const int slice = (int)(u / KT);
@@ -104,269 +235,370 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
     const int len = kt1 - kt0;
     const int wb = kt0 + (int)((long long)len * warp / kStreamWarps);
     const int we = kt0 + (int)((long long)len * (warp + 1) / kStreamWarps);
+    const int n_steps = we - wb;
 
-    float acc[MB][NTW][8][4];
+    // acc[mt][j][sub][el]: column 64 j + 16 sub + c8 + 8 (el >> 1), row 8 mt + 2 q + (el & 1)
+    float acc[MT][NTW][4][4];  // scaled sums (kGrouped) / running sums (kChannel)
+    float grp[GM == kGrouped ? MT : 1][GM == kGrouped ? NTW : 1][4][4];  // sums of the open group
+    float corr[MT][4], rsum[MT][4];
 #pragma unroll
-    for (int i = 0; i < MB; ++i)
+    for (int i = 0; i < MT; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) corr[i][e] = rsum[i][e] = 0.f;
 #pragma unroll
       for (int j = 0; j < NTW; ++j)
 #pragma unroll
-        for (int b = 0; b < 8; ++b)
+        for (int b = 0; b < 4; ++b)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) acc[i][j][b][e] = 0.f;
+          for (int e = 0; e < 4; ++e) {
+            acc[i][j][b][e] = 0.f;
+            if constexpr (GM == kGrouped) grp[i][j][b][e] = 0.f;
+          }
+    }
 
-    // ---- producer: one ring stage = weights + A tile (+ scales, zeros) of one k-tile
-    // scales (kGrouped) and zero-points ride in the stage of the first k-tile
-    // of a group, and of the warp's first k-tile
-    auto has_scales = [&](int kt) {
-      return (GM == kGrouped || HAS_ZP) && (kt == wb || kt % p.group_blocks == 0);
-    };
-    auto issue = [&](int kt, int stage) {
-      const uint32_t st = ring + stage * Cfg::kStageBytes;
-      if (kt < we) {
-        const uint4* wsrc =
-            reinterpret_cast<const uint4*>(p.b) + ((size_t)kt * NT + nt0) * (Cfg::kTileBytes / 16);
+    // ---- producer state -------------------------------------------------------------
+    const unsigned char* i_w = reinterpret_cast<const unsigned char*>(p.b) +
+                               ((size_t)wb * NT + nt0) * Cfg::kTileBytes + lane * 16;
+    const unsigned char* i_a = static_cast<const unsigned char*>(p.a) +
+                               ((size_t)(a_bytes[0] ? fr : 0) * p.lda + (size_t)wb * 16 + fh * 8) * 2;
+    uint32_t i_st = ring;  // next stage to fill
+    const uint32_t ring_end = ring + D * Cfg::kStageBytes;
+    const int gb = p.group_blocks;
+    int i_g = (GM == kGrouped) ? wb / gb : 0;  // group of the next k-tile to issue
+    int i_left = 0;                            // k-tiles until the next group load
+    int i_first_left = (GM == kGrouped) ? gb - wb % gb : 0;
+    int issued = 0;
+
+    auto issue = [&]() {
 #pragma unroll
-        for (int j = 0; j < NTW; ++j) {
-          if (BITS == 4) {
-            cp_async16(st + Cfg::kWOff + j * 512 + lane * 16, wsrc + j * 32 + lane);
-          } else {
-            // chunk ch of the tile belongs to lane ch/2, half ch%2
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int ch = lane + 32 * h;
-              cp_async16(st + Cfg::kWOff + j * 1024 + (ch & 1) * 512 + (ch >> 1) * 16,
-                         wsrc + j * 64 + ch);
-            }
-          }
+      for (int j = 0; j < NTW; ++j) {
+        if (BITS == 4) {
+          cp_async16(i_st + j * 512 + lane * 16, i_w + j * 512);
+        } else {
+          // 16 B chunk ch of a tile belongs to lane ch/2, half ch%2
+          cp_async16(i_st + j * 1024 + (lane & 1) * 512 + (lane >> 1) * 16, i_w + j * 1024);
+          cp_async16(i_st + j * 1024 + (lane & 1) * 512 + (16 + (lane >> 1)) * 16,
+                     i_w + j * 1024 + 512);
         }
-        {
-          const int r = lane >> 1, h = lane & 1;
-          const int pos = 2 * r + (h ^ ((r >> 2) & 1));
+      }
 #pragma unroll
-          for (int i = 0; i < MB; ++i) {
-            const int row = i * 16 + r;
-            const bool ok = row < p.m;
-            const uint16_t* src = A + (size_t)(ok ? row : 0) * p.lda + kt * 16 + h * 8;
-            cp_async16(st + Cfg::kAOff + i * 512 + pos * 16, src, ok ? 16 : 0);
-          }
-        }
-        if (has_scales(kt)) {
-          const int g = kt / p.group_blocks;
-          if (GM == kGrouped && lane < NTW * 8)
-            cp_async16(st + Cfg::kSOff + lane * 16, S + (size_t)g * p.n + nt0 * 64 + lane * 8);
+      for (int i = 0; i < kABlocks; ++i)
+        cp_async16(i_st + Cfg::kAOff + i * 512 + a_fill_off,
+                   a_bytes[i] ? i_a + i * a_blk_stride : i_a, a_bytes[i]);
+      if (GM == kGrouped) {
+        if (i_left == 0) {
+          const uint32_t slot = slots + (i_g & (Cfg::kSlots - 1)) * Cfg::kSlotBytes;
+          // NTW * 8 chunks of scales; surplus lanes repeat a chunk instead of diverging
+          const int sl = lane & (NTW * 8 - 1);
+          cp_async16(slot + sl * 16, S + (size_t)i_g * p.n + nt0 * 64 + sl * 8);
           if (HAS_ZP) {
             constexpr int kChunks = NTW * 8 * BITS / 16;  // 16 B chunks of zero-point words
-            if (lane < kChunks)
-              cp_async16(st + Cfg::kZOff + lane * 16,
-                         p.zeros + (size_t)g * (p.n * BITS / 32) + nt0 * (2 * BITS) + lane * 4);
+            const int zl = lane & (kChunks - 1);
+            cp_async16(slot + Cfg::kSlotZOff + zl * 16,
+                       p.zeros + (size_t)i_g * (p.n * BITS / 32) + nt0 * (2 * BITS) + zl * 4);
+          }
+          ++i_g;
+          i_left = i_first_left;
+          i_first_left = gb;
+        }
+        --i_left;
+      }
+      i_w += w_kt_stride;
+      i_a += 32;
+      i_st += Cfg::kStageBytes;
+      if (i_st == ring_end) i_st = ring;
+    };
+
+    // ---- group end: fold the open group's sums into acc ---------------------------------
+    auto close_group = [&](int g) {
+      if constexpr (GM == kGrouped) {
+        const uint32_t slot = slots + (g & (Cfg::kSlots - 1)) * Cfg::kSlotBytes;
+#pragma unroll
+        for (int j = 0; j < NTW; ++j) {
+          // chunk c8 of the permuted scale row: columns c8 + 8 jj, jj = 2 sub + (el >> 1)
+          const uint4 c0 = lds128(slot + j * 128 + c8 * 16);
+          const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
+          uint32_t zw[2];
+          (void)zw;
+          if (HAS_ZP) {
+            if (BITS == 4) {
+              zw[0] = lds32(slot + Cfg::kSlotZOff + j * 32 + c8 * 4);
+            } else {
+              zw[0] = lds32(slot + Cfg::kSlotZOff + j * 64 + c8 * 8);
+              zw[1] = lds32(slot + Cfg::kSlotZOff + j * 64 + c8 * 8 + 4);
+            }
+          }
+#pragma unroll
+          for (int sub = 0; sub < 4; ++sub) {
+            float sc[2], zf[2];
+            sc[0] = lo16_to_float<T>(cw[sub]);
+            sc[1] = hi16_to_float<T>(cw[sub]);
+            if (HAS_ZP) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int jj = 2 * sub + h;
+                if (BITS == 4) {
+                  // column c8 + 8 jj sits at nibble [0,4,1,5,2,6,3,7][jj]
+                  const int t = (jj >> 1) + 4 * (jj & 1);
+                  zf[h] = (float)((zw[0] >> (4 * t)) & 15u);
+                } else {
+                  // word jj/4, byte [0,2,1,3][jj%4]
+                  const int t = ((jj & 1) << 1) | ((jj >> 1) & 1);
+                  zf[h] = (float)((zw[jj >> 2] >> (8 * t)) & 255u);
+                }
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+              for (int el = 0; el < 4; ++el) {
+                float v = grp[i][j][sub][el];
+                if (E::kEmbed) v -= corr[i][el & 1];
+                if (HAS_ZP) v = fmaf(-zf[el >> 1], rsum[i][el & 1], v);
+                acc[i][j][sub][el] = fmaf(sc[el >> 1], v, acc[i][j][sub][el]);
+                grp[i][j][sub][el] = 0.f;
+              }
           }
         }
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) corr[i][e] = rsum[i][e] = 0.f;
+      }
+    };
+
+#pragma unroll
+    for (int s = 0; s < D - 1; ++s) {
+      if (issued < n_steps) {
+        issue();
+        ++issued;
       }
       cp_async_commit();
-    };
+    }
 
-    // scale / zero-point state carried across k-tiles of a group
-    uint32_t sdup[NTW][8];
-    uint32_t zdup[NTW][8];
-    (void)sdup;
-    (void)zdup;
+    uint32_t c_st = ring;
+    int c_g = (GM == kGrouped) ? wb / gb : 0;
+    int c_left = (GM == kGrouped) ? gb - wb % gb : 0;
 
-    auto load_group_from_stage = [&](uint32_t st) {
-#pragma unroll
-      for (int j = 0; j < NTW; ++j) {
-        if (GM == kGrouped) {
-          const uint4 s4 = lds128(st + Cfg::kSOff + j * 128 + c8 * 16);
-          const uint32_t sv[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-          for (int sub = 0; sub < 4; ++sub) {
-            sdup[j][2 * sub] = dup_lo(sv[sub]);
-            sdup[j][2 * sub + 1] = dup_hi(sv[sub]);
-          }
-        }
-        if (HAS_ZP) {
-          uint32_t zp[4];
-          if (BITS == 4) {
-            dequant4<T, false>(lds32(st + Cfg::kZOff + j * 32 + c8 * 4), zp);
-          } else {
-            uint32_t t0[2], t1[2];
-            dequant8<T, false>(lds32(st + Cfg::kZOff + j * 64 + c8 * 8), t0);
-            dequant8<T, false>(lds32(st + Cfg::kZOff + j * 64 + c8 * 8 + 4), t1);
-            zp[0] = t0[0]; zp[1] = t0[1]; zp[2] = t1[0]; zp[3] = t1[1];
-          }
-#pragma unroll
-          for (int sub = 0; sub < 4; ++sub) {
-            zdup[j][2 * sub] = dup_lo(zp[sub]);
-            zdup[j][2 * sub + 1] = dup_hi(zp[sub]);
-          }
-        }
-      }
-    };
-
-    // kLookup: group of every row this lane touches, straight from global memory
-    auto load_group_lookup = [&](int kt, int j, uint32_t (&s_rows)[4][4]) {
-      const int q = lane & 3;
-      const int rows[4] = {2 * q, 2 * q + 1, 2 * q + 8, 2 * q + 9};
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int g = p.g_idx[kt * 16 + rows[r]];
-        const uint4 s4 = *reinterpret_cast<const uint4*>(S + (size_t)g * p.n + (nt0 + j) * 64 + c8 * 8);
-        s_rows[r][0] = s4.x; s_rows[r][1] = s4.y; s_rows[r][2] = s4.z; s_rows[r][3] = s4.w;
-      }
-    };
-
-#pragma unroll
-    for (int s = 0; s < D - 1; ++s) issue(wb + s, s);
-
-    for (int kt = wb; kt < we; ++kt) {
-      const int stage = (kt - wb) % D;
+    for (int s = 0; s < n_steps; ++s) {
       cp_async_wait<D - 2>();
       __syncwarp();
-      issue(kt + D - 1, (kt - wb + D - 1) % D);
-      const uint32_t st = ring + stage * Cfg::kStageBytes;
+      if (issued < n_steps) {
+        issue();
+        ++issued;
+      }
+      cp_async_commit();
+      const uint32_t st = c_st;
+      c_st += Cfg::kStageBytes;
+      if (c_st == ring_end) c_st = ring;
 
-      if (has_scales(kt)) load_group_from_stage(st);
-
-      uint32_t afrag[MB][4];
-      {
-        const int r = (lane & 7) + 8 * ((lane >> 3) & 1), h = lane >> 4;
-        const int pos = 2 * r + (h ^ ((r >> 2) & 1));
+      // activations: act[mt][0] = k 0..7, act[mt][1] = k 8..15 of 8 rows
+      uint32_t act[MT][2];
+      if constexpr (MT == 1) {
+        ldmatrix_x2(act[0][0], act[0][1], st + Cfg::kAOff + a_ld_off);
+      } else {
 #pragma unroll
-        for (int i = 0; i < MB; ++i) ldmatrix_x4(afrag[i], st + Cfg::kAOff + i * 512 + pos * 16);
+        for (int i = 0; i < MT / 2; ++i) {
+          uint32_t r[4];
+          ldmatrix_x4(r, st + Cfg::kAOff + i * 512 + a_ld_off);
+          act[2 * i][0] = r[0]; act[2 * i][1] = r[1];
+          act[2 * i + 1][0] = r[2]; act[2 * i + 1][1] = r[3];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        if (E::kPrescale) act[i][1] = Pair<T>::mul(act[i][1], E::kAScaleHi);
+        if (E::kEmbed) {
+          const uint32_t off[4] = {kBiased ? E::kOffLoBiased : E::kOffLoRaw,
+                                   kBiased ? E::kOffLoBiased : E::kOffLoRaw,
+                                   kBiased ? E::kOffHiBiased : E::kOffHiRaw,
+                                   kBiased ? E::kOffHiBiased : E::kOffHiRaw};
+          mma16816<T>(corr[i], off, act[i][0], act[i][1]);
+        }
+        if (HAS_ZP) {
+          const uint32_t one[4] = {E::kOneLo, E::kOneLo, E::kOneHi, E::kOneHi};
+          mma16816<T>(rsum[i], one, act[i][0], act[i][1]);
+        }
       }
 
 #pragma unroll
       for (int j = 0; j < NTW; ++j) {
-        uint32_t s_rows[4][4];
-        (void)s_rows;
-        if (GM == kLookup) load_group_lookup(kt, j, s_rows);
-
-        uint32_t w[BITS == 4 ? 4 : 8];
+        uint32_t w[kWordsPerTile];
         {
-          const uint4 w4 = lds128(st + Cfg::kWOff + j * Cfg::kTileBytes + lane * 16);
+          const uint4 w4 = lds128(st + j * Cfg::kTileBytes + lane * 16);
           w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
           if (BITS == 8) {
-            const uint4 w5 = lds128(st + Cfg::kWOff + j * Cfg::kTileBytes + 512 + lane * 16);
+            const uint4 w5 = lds128(st + j * Cfg::kTileBytes + 512 + lane * 16);
             w[4] = w5.x; w[5] = w5.y; w[6] = w5.z; w[7] = w5.w;
           }
         }
 #pragma unroll
         for (int sub = 0; sub < 4; ++sub) {
-          uint32_t f[4];  // block 0: f[0] rows lo, f[1] rows hi; block 1: f[2], f[3]
-          if (BITS == 4) {
-            dequant4<T, !HAS_ZP>(w[sub], f);
-          } else {
-            uint32_t t0[2], t1[2];
-            dequant8<T, !HAS_ZP>(w[2 * sub], t0);
-            dequant8<T, !HAS_ZP>(w[2 * sub + 1], t1);
-            f[0] = t0[0]; f[1] = t0[1]; f[2] = t1[0]; f[3] = t1[1];
-          }
-          if (HAS_ZP) {
-            f[0] = Pair<T>::sub(f[0], zdup[j][2 * sub]);
-            f[1] = Pair<T>::sub(f[1], zdup[j][2 * sub]);
-            f[2] = Pair<T>::sub(f[2], zdup[j][2 * sub + 1]);
-            f[3] = Pair<T>::sub(f[3], zdup[j][2 * sub + 1]);
-          }
-          if (GM == kGrouped) {
-            f[0] = Pair<T>::mul(f[0], sdup[j][2 * sub]);
-            f[1] = Pair<T>::mul(f[1], sdup[j][2 * sub]);
-            f[2] = Pair<T>::mul(f[2], sdup[j][2 * sub + 1]);
-            f[3] = Pair<T>::mul(f[3], sdup[j][2 * sub + 1]);
-          } else if (GM == kLookup) {
-            // pair (row lo, row lo+1) of block 0 uses scale word `sub` low halves
-            // of those two rows; block 1 the high halves
-            const uint32_t s00 = __byte_perm(s_rows[0][sub], s_rows[1][sub], 0x5410);
-            const uint32_t s01 = __byte_perm(s_rows[2][sub], s_rows[3][sub], 0x5410);
-            const uint32_t s10 = __byte_perm(s_rows[0][sub], s_rows[1][sub], 0x7632);
-            const uint32_t s11 = __byte_perm(s_rows[2][sub], s_rows[3][sub], 0x7632);
-            f[0] = Pair<T>::mul(f[0], s00);
-            f[1] = Pair<T>::mul(f[1], s01);
-            f[2] = Pair<T>::mul(f[2], s10);
-            f[3] = Pair<T>::mul(f[3], s11);
-          }
+          uint32_t f[4];
+          expand<T, BITS, kBiased>(w, sub, ex, mlo, mhi, f);
 #pragma unroll
-          for (int i = 0; i < MB; ++i) {
-            mma16816<T>(acc[i][j][2 * sub], afrag[i], f[0], f[1]);
-            mma16816<T>(acc[i][j][2 * sub + 1], afrag[i], f[2], f[3]);
+          for (int i = 0; i < MT; ++i) {
+            if constexpr (GM == kGrouped)
+              mma16816<T>(grp[i][j][sub], f, act[i][0], act[i][1]);
+            else
+              mma16816<T>(acc[i][j][sub], f, act[i][0], act[i][1]);
           }
+        }
+      }
+
+      if (GM == kGrouped) {
+        if (--c_left == 0 || s == n_steps - 1) {
+          close_group(c_g);
+          ++c_g;
+          c_left = gb;
         }
       }
     }
     cp_async_wait<0>();
 
-    // ---- intra-CTA reduction, one 16-row block at a time -------------------------
+    if constexpr (GM == kChannel) {
+      // remove the offset (and zero-point) terms once, at the end of the warp's range
+      if (E::kEmbed || HAS_ZP) {
+#pragma unroll
+        for (int j = 0; j < NTW; ++j) {
+          uint32_t zw[2];
+          (void)zw;
+          if (HAS_ZP) {
+            const uint32_t* zrow = p.zeros + (size_t)(nt0 + j) * (2 * BITS);
+            if (BITS == 4) {
+              zw[0] = __ldg(zrow + c8);
+            } else {
+              zw[0] = __ldg(zrow + 2 * c8);
+              zw[1] = __ldg(zrow + 2 * c8 + 1);
+            }
+          }
+#pragma unroll
+          for (int sub = 0; sub < 4; ++sub) {
+            float zf[2] = {0.f, 0.f};
+            if (HAS_ZP) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const int jj = 2 * sub + h;
+                if (BITS == 4) {
+                  const int t = (jj >> 1) + 4 * (jj & 1);
+                  zf[h] = (float)((zw[0] >> (4 * t)) & 15u);
+                } else {
+                  const int t = ((jj & 1) << 1) | ((jj >> 1) & 1);
+                  zf[h] = (float)((zw[jj >> 2] >> (8 * t)) & 255u);
+                }
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+              for (int el = 0; el < 4; ++el) {
+                float v = acc[i][j][sub][el];
+                if (E::kEmbed) v -= corr[i][el & 1];
+                if (HAS_ZP) v = fmaf(-zf[el >> 1], rsum[i][el & 1], v);
+                acc[i][j][sub][el] = v;
+              }
+          }
+        }
+      }
+    }
+
+    // ---- intra-CTA reduction, one 8-row block at a time ----------------------------
     const long long s_first_u = (long long)slice * KT;
     const int first_cta = (int)(((s_first_u + 1) * gridDim.x - 1) / total);
     const int last_cta = (int)(((s_first_u + KT) * gridDim.x - 1) / total);
     const bool split = first_cta != last_cta;
 
-    float outv[MB][Cfg::kEpt];
-    const int o_row = threadIdx.x >> 4;                // 0..15
-    const int o_col = (threadIdx.x & 15) * Cfg::kEpt;  // inside the slice
+    float outv[MT][Cfg::kEpt];
+    const int o_row = threadIdx.x >> 5;                // 0..7
+    const int o_col = (threadIdx.x & 31) * Cfg::kEpt;  // inside the slice
 #pragma unroll
-    for (int i = 0; i < MB; ++i) {
+    for (int i = 0; i < MT; ++i) {
       __syncthreads();  // ring (or previous block's sums) no longer in use
       {
-        float* mine = red + warp * (16 * Cfg::kRedStride);
-        const int q = lane & 3;
+        float* mine = red + warp * (8 * Cfg::kRedStride);
 #pragma unroll
         for (int j = 0; j < NTW; ++j)
 #pragma unroll
-          for (int b = 0; b < 8; ++b) {
-            const int col = j * 64 + b * 8 + 2 * q;
-            *reinterpret_cast<float2*>(mine + c8 * Cfg::kRedStride + col) =
-                make_float2(acc[i][j][b][0], acc[i][j][b][1]);
-            *reinterpret_cast<float2*>(mine + (c8 + 8) * Cfg::kRedStride + col) =
-                make_float2(acc[i][j][b][2], acc[i][j][b][3]);
-          }
+          for (int sub = 0; sub < 4; ++sub)
+#pragma unroll
+            for (int el = 0; el < 4; ++el)
+              mine[(2 * q + (el & 1)) * Cfg::kRedStride + j * 64 + sub * 16 + c8 + 8 * (el >> 1)] =
+                  acc[i][j][sub][el];
       }
       __syncthreads();
 #pragma unroll
       for (int e = 0; e < Cfg::kEpt; ++e) outv[i][e] = 0.f;
 #pragma unroll
       for (int w8 = 0; w8 < kStreamWarps; ++w8) {
-        const float* src = red + w8 * (16 * Cfg::kRedStride) + o_row * Cfg::kRedStride + o_col;
-#pragma unroll
-        for (int e = 0; e < Cfg::kEpt; e += 4) {
-          const float4 v = *reinterpret_cast<const float4*>(src + e);
-          outv[i][e] += v.x; outv[i][e + 1] += v.y; outv[i][e + 2] += v.z; outv[i][e + 3] += v.w;
+        const float* src = red + w8 * (8 * Cfg::kRedStride) + o_row * Cfg::kRedStride + o_col;
+        if constexpr (Cfg::kEpt == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(src);
+          outv[i][0] += v.x; outv[i][1] += v.y; outv[i][2] += v.z; outv[i][3] += v.w;
+        } else {
+          const float2 v = *reinterpret_cast<const float2*>(src);
+          outv[i][0] += v.x; outv[i][1] += v.y;
         }
       }
     }
 
     // ---- cross-CTA reduction for split slices --------------------------------------
+    auto slot_ptr = [&](int cta, int i) {
+      return p.partials + (size_t)(cta + slice) * Cfg::kSlotFloats + (i * 8 + o_row) * (64 * NTW) +
+             o_col;
+    };
     bool do_store = true;
     if (split) {
-      float* slot = p.partials + (size_t)(blockIdx.x + slice) * Cfg::kSlotFloats;
 #pragma unroll
-      for (int i = 0; i < MB; ++i)
-#pragma unroll
-        for (int e = 0; e < Cfg::kEpt; e += 4)
-          __stcg(reinterpret_cast<float4*>(slot + (i * 16 + o_row) * (64 * NTW) + o_col + e),
-                 make_float4(outv[i][e], outv[i][e + 1], outv[i][e + 2], outv[i][e + 3]));
-      __threadfence();
-      __syncthreads();
+      for (int i = 0; i < MT; ++i) {
+        if constexpr (Cfg::kEpt == 4)
+          __stcg(reinterpret_cast<float4*>(slot_ptr(blockIdx.x, i)),
+                 make_float4(outv[i][0], outv[i][1], outv[i][2], outv[i][3]));
+        else
+          __stcg(reinterpret_cast<float2*>(slot_ptr(blockIdx.x, i)),
+                 make_float2(outv[i][0], outv[i][1]));
+      }
+      __syncthreads();  // all of this CTA's partial is written ...
       if (threadIdx.x == 0) {
-        const int prev = atomicAdd(p.counters + first_cta, 1);
+        // ... and released, with the other CTAs' partials acquired, by one gpu-scope RMW
+        int prev;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n"
+                     : "=r"(prev)
+                     : "l"(p.counters + first_cta)
+                     : "memory");
         s_is_last = (prev == last_cta - first_cta);
       }
       __syncthreads();
       do_store = s_is_last != 0;
       if (do_store) {
-        __threadfence();
 #pragma unroll
-        for (int i = 0; i < MB; ++i)
+        for (int i = 0; i < MT; ++i)
 #pragma unroll
           for (int e = 0; e < Cfg::kEpt; ++e) outv[i][e] = 0.f;
-        for (int cta = first_cta; cta <= last_cta; ++cta) {
-          const float* src = p.partials + (size_t)(cta + slice) * Cfg::kSlotFloats;
+        // fixed summation order (CTA order); loads of 4 partials are in flight at a time
+        constexpr int kBatch = 4;
+        for (int cta = first_cta; cta <= last_cta; cta += kBatch) {
+          float v[kBatch][MT][Cfg::kEpt];
 #pragma unroll
-          for (int i = 0; i < MB; ++i)
+          for (int t = 0; t < kBatch; ++t) {
+            const int src_cta = min(cta + t, last_cta);
 #pragma unroll
-            for (int e = 0; e < Cfg::kEpt; e += 4) {
-              const float4 v = __ldcg(
-                  reinterpret_cast<const float4*>(src + (i * 16 + o_row) * (64 * NTW) + o_col + e));
-              outv[i][e] += v.x; outv[i][e + 1] += v.y; outv[i][e + 2] += v.z; outv[i][e + 3] += v.w;
+            for (int i = 0; i < MT; ++i) {
+              if constexpr (Cfg::kEpt == 4) {
+                const float4 x = __ldcg(reinterpret_cast<const float4*>(slot_ptr(src_cta, i)));
+                v[t][i][0] = x.x; v[t][i][1] = x.y; v[t][i][2] = x.z; v[t][i][3] = x.w;
+              } else {
+                const float2 x = __ldcg(reinterpret_cast<const float2*>(slot_ptr(src_cta, i)));
+                v[t][i][0] = x.x; v[t][i][1] = x.y;
+              }
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < kBatch; ++t)
+            if (cta + t <= last_cta) {
+#pragma unroll
+              for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int e = 0; e < Cfg::kEpt; ++e) outv[i][e] += v[t][i][e];
             }
         }
         if (threadIdx.x == 0) p.counters[first_cta] = 0;
@@ -386,21 +618,22 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
       }
       uint16_t* C = static_cast<uint16_t*>(p.c);
 #pragma unroll
-      for (int i = 0; i < MB; ++i) {
-        const int row = i * 16 + o_row;
+      for (int i = 0; i < MT; ++i) {
+        const int row = i * 8 + o_row;
         if (row < p.m) {
           uint32_t packed[Cfg::kEpt / 2];
 #pragma unroll
           for (int e = 0; e < Cfg::kEpt; e += 2) {
             const float v0 = outv[i][e] * cs[e] + bs[e];
             const float v1 = outv[i][e + 1] * cs[e + 1] + bs[e + 1];
-            packed[e / 2] = (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
+            packed[e / 2] =
+                (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
           }
           uint16_t* dst = C + (size_t)row * p.n + n_base;
-          if (Cfg::kEpt == 8)
-            *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          else
+          if constexpr (Cfg::kEpt == 4)
             *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[1]);
+          else
+            *reinterpret_cast<uint32_t*>(dst) = packed[0];
         }
       }
     }
@@ -408,12 +641,15 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
   }
 }
 
-// Host launcher for one (type, bits, zp, group mode, MB, NTW) variant.
-template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW>
-int launch_stream(const StreamParams& p, int max_ctas, cudaStream_t stream) {
-  using Cfg = StreamCfg<BITS, HAS_ZP, GM, MB, NTW>;
-  constexpr int kMinBlocks = (MB * NTW <= 2 && Cfg::kSmemBytes <= 112 * 1024) ? 2 : 1;
-  auto kernel = gemm_stream_kernel<T, BITS, HAS_ZP, GM, MB, NTW, kMinBlocks>;
+// Host launcher for one (type, bits, zp, group mode, MT, NTW) variant.
+template <typename T, int BITS, bool HAS_ZP, int GM, int MT, int NTW>
+int launch_stream(StreamParams p, int max_ctas, cudaStream_t stream) {
+  using Cfg = StreamCfg<BITS, HAS_ZP, GM, MT, NTW>;
+  using E = Emb<T, BITS>;
+  // accumulator registers: acc (+ grp when grouped)
+  constexpr int kAccRegs = MT * NTW * 16 * (GM == kGrouped ? 2 : 1);
+  constexpr int kMinBlocks = (kAccRegs <= 64 && MT <= 2 && Cfg::kSmemBytes <= 112 * 1024) ? 2 : 1;
+  auto kernel = gemm_stream_kernel<T, BITS, HAS_ZP, GM, MT, NTW, kMinBlocks>;
   static bool attr_done[64] = {};  // per device; benign race: the call is idempotent
   int dev = 0;
   B200Q_CUDA_OK(cudaGetDevice(&dev));
@@ -422,6 +658,9 @@ int launch_stream(const StreamParams& p, int max_ctas, cudaStream_t stream) {
                                        Cfg::kSmemBytes));
     attr_done[dev & 63] = true;
   }
+  p.c_ex = E::kEx;
+  p.c_mask_lo = E::kMaskLo;
+  p.c_mask_hi = E::kMaskHi;
   const long long total = (long long)p.slices * p.kt_total;
   long long want = (long long)device_sm_count() * kMinBlocks;
   if (want > max_ctas) want = max_ctas;
@@ -432,12 +671,5 @@ int launch_stream(const StreamParams& p, int max_ctas, cudaStream_t stream) {
   B200Q_CUDA_OK(cudaGetLastError());
   return B200Q_OK;
 }
-
-// Defined in gemm_stream_inst_*.cu: dispatch on (MB, NTW) for a fixed (T, BITS).
-template <typename T, int BITS>
-int dispatch_stream(const StreamParams& p, bool has_zp, int gm, int mb, int ntw, int max_ctas,
-                    cudaStream_t stream);
-
-size_t stream_partial_floats(int mb, int ntw);
 
 }  // namespace b200q

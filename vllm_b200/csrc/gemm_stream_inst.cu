@@ -1,6 +1,7 @@
-// Instantiations of the streaming GEMM for one (element type, weight bits)
-// pair, selected at compile time with -DINST_BF16={0,1} -DINST_BITS={4,8} so
-// that the four translation units build in parallel.
+// Instantiations of the decode-regime GEMM kernels for one (element type,
+// weight bits) pair, selected at compile time with -DINST_BF16={0,1}
+// -DINST_BITS={4,8} so that the four translation units build in parallel.
+#include "gemm_lookup.cuh"
 #include "gemm_stream.cuh"
 
 #ifndef INST_BF16
@@ -15,30 +16,53 @@ using InstT = __nv_bfloat16;
 using InstT = half;
 #endif
 
+template <typename T, int BITS>
+int dispatch_stream(const StreamParams& p, bool has_zp, int gm, int mb, int ntw, int max_ctas,
+                    cudaStream_t stream);
+
 namespace {
 
-template <bool HAS_ZP, int GM>
-int by_shape(const StreamParams& p, int mb, int ntw, int max_ctas, cudaStream_t stream) {
-  using T = InstT;
-  constexpr int B = INST_BITS;
-  if constexpr (GM == kLookup) {  // slow path: one tile width only
-    if (ntw != 1) return B200Q_EUNSUPPORTED;
-    switch (mb) {
-      case 1: return launch_stream<T, B, HAS_ZP, GM, 1, 1>(p, max_ctas, stream);
-      case 2: return launch_stream<T, B, HAS_ZP, GM, 2, 1>(p, max_ctas, stream);
-      case 4: return launch_stream<T, B, HAS_ZP, GM, 4, 1>(p, max_ctas, stream);
-    }
-    return B200Q_EUNSUPPORTED;
-  } else {
-    switch (mb * 10 + ntw) {
-      case 11: return launch_stream<T, B, HAS_ZP, GM, 1, 1>(p, max_ctas, stream);
-      case 12: return launch_stream<T, B, HAS_ZP, GM, 1, 2>(p, max_ctas, stream);
-      case 21: return launch_stream<T, B, HAS_ZP, GM, 2, 1>(p, max_ctas, stream);
-      case 22: return launch_stream<T, B, HAS_ZP, GM, 2, 2>(p, max_ctas, stream);
-      case 41: return launch_stream<T, B, HAS_ZP, GM, 4, 1>(p, max_ctas, stream);
-    }
-    return B200Q_EUNSUPPORTED;
+using T = InstT;
+constexpr int B = INST_BITS;
+
+// `rows8` = 8-row blocks of A (1, 2, 4, 8); 8 blocks (64 rows) hold too many
+// accumulators for the streaming kernel and run the reference-order kernel.
+template <bool HAS_ZP>
+int channel(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
+  switch (rows8 * 10 + ntw) {
+    case 11: return launch_stream<T, B, HAS_ZP, kChannel, 1, 1>(p, max_ctas, stream);
+    case 12: return launch_stream<T, B, HAS_ZP, kChannel, 1, 2>(p, max_ctas, stream);
+    case 21: return launch_stream<T, B, HAS_ZP, kChannel, 2, 1>(p, max_ctas, stream);
+    case 22: return launch_stream<T, B, HAS_ZP, kChannel, 2, 2>(p, max_ctas, stream);
+    case 41: return launch_stream<T, B, HAS_ZP, kChannel, 4, 1>(p, max_ctas, stream);
+    case 42: return launch_stream<T, B, HAS_ZP, kChannel, 4, 2>(p, max_ctas, stream);
+    case 81: return launch_lookup<T, B, HAS_ZP, kChannel, 4, 1>(p, max_ctas, stream);
   }
+  return B200Q_EUNSUPPORTED;
+}
+
+template <bool HAS_ZP>
+int grouped(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
+  switch (rows8 * 10 + ntw) {
+    case 11: return launch_stream<T, B, HAS_ZP, kGrouped, 1, 1>(p, max_ctas, stream);
+    case 12: return launch_stream<T, B, HAS_ZP, kGrouped, 1, 2>(p, max_ctas, stream);
+    case 21: return launch_stream<T, B, HAS_ZP, kGrouped, 2, 1>(p, max_ctas, stream);
+    case 22: return launch_stream<T, B, HAS_ZP, kGrouped, 2, 2>(p, max_ctas, stream);
+    case 41: return launch_stream<T, B, HAS_ZP, kGrouped, 4, 1>(p, max_ctas, stream);
+    case 81: return launch_lookup<T, B, HAS_ZP, kGrouped, 4, 1>(p, max_ctas, stream);
+  }
+  return B200Q_EUNSUPPORTED;
+}
+
+int lookup(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
+  if (ntw != 1) return B200Q_EUNSUPPORTED;
+  const int mb = (rows8 + 1) / 2;  // 16-row blocks
+  switch (mb) {
+    case 1: return launch_lookup<T, B, false, kLookup, 1, 1>(p, max_ctas, stream);
+    case 2: return launch_lookup<T, B, false, kLookup, 2, 1>(p, max_ctas, stream);
+    case 4: return launch_lookup<T, B, false, kLookup, 4, 1>(p, max_ctas, stream);
+  }
+  return B200Q_EUNSUPPORTED;
 }
 
 }  // namespace
@@ -46,14 +70,14 @@ int by_shape(const StreamParams& p, int mb, int ntw, int max_ctas, cudaStream_t 
 template <>
 int dispatch_stream<InstT, INST_BITS>(const StreamParams& p, bool has_zp, int gm, int mb, int ntw,
                                       int max_ctas, cudaStream_t stream) {
-  if (has_zp) {
-    if (gm == kChannel) return by_shape<true, kChannel>(p, mb, ntw, max_ctas, stream);
-    if (gm == kGrouped) return by_shape<true, kGrouped>(p, mb, ntw, max_ctas, stream);
-    return B200Q_EUNSUPPORTED;
-  }
-  if (gm == kChannel) return by_shape<false, kChannel>(p, mb, ntw, max_ctas, stream);
-  if (gm == kGrouped) return by_shape<false, kGrouped>(p, mb, ntw, max_ctas, stream);
-  return by_shape<false, kLookup>(p, mb, ntw, max_ctas, stream);
+  if (gm == kChannel)
+    return has_zp ? channel<true>(p, mb, ntw, max_ctas, stream)
+                  : channel<false>(p, mb, ntw, max_ctas, stream);
+  if (gm == kGrouped)
+    return has_zp ? grouped<true>(p, mb, ntw, max_ctas, stream)
+                  : grouped<false>(p, mb, ntw, max_ctas, stream);
+  if (has_zp) return B200Q_EUNSUPPORTED;
+  return lookup(p, mb, ntw, max_ctas, stream);
 }
 
 }  // namespace b200q
