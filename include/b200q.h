@@ -49,6 +49,11 @@ int b200q_version(void);
  * GEMM workspace from this (marlin_utils.py:237-245). */
 int b200q_sm_count(void);
 
+/* Number of kernels this library has launched in the process so far (all
+ * entry points, all threads).  Lets a caller count the launches of a timed
+ * region.  No counterpart in the reference. */
+unsigned long long b200q_kernel_launches(void);
+
 /*
  * GPTQ checkpoint layout -> Marlin tile layout.
  * Replaces: gptq_marlin_repack, csrc/quantization/gptq_marlin/gptq_marlin_repack.cu:251-322

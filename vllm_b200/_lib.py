@@ -16,6 +16,7 @@ EXPORTS = (
     "b200q_last_error",
     "b200q_version",
     "b200q_sm_count",
+    "b200q_kernel_launches",
     "b200q_gptq_marlin_repack",
     "b200q_awq_marlin_repack",
     "b200q_permute_cols",
@@ -52,6 +53,8 @@ def load() -> ctypes.CDLL:
     lib.b200q_last_error.argtypes = []
     lib.b200q_version.restype = i32
     lib.b200q_sm_count.restype = i32
+    lib.b200q_kernel_launches.restype = c.c_ulonglong
+    lib.b200q_kernel_launches.argtypes = []
     lib.b200q_gptq_marlin_repack.restype = i32
     lib.b200q_gptq_marlin_repack.argtypes = [vp, vp, vp, i64, i64, i32, vp]
     lib.b200q_awq_marlin_repack.restype = i32

@@ -1,6 +1,7 @@
 // extern "C" surface of libb200q: argument validation (mirroring the checks of
 // the reference op, csrc/quantization/gptq_marlin/gptq_marlin.cu:688-902), kernel
 // selection and scratch accounting.  No torch types cross this boundary.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -14,6 +15,9 @@ thread_local char g_error[512] = "";
 int g_sm_count[64];
 int g_smem_optin[64];
 }  // namespace
+
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -85,6 +89,7 @@ using namespace b200q;
 
 extern "C" const char* b200q_last_error(void) { return g_error; }
 extern "C" int b200q_version(void) { return 100; }
+extern "C" unsigned long long b200q_kernel_launches(void) { return g_launches.load(); }
 extern "C" int b200q_sm_count(void) { return device_sm_count(); }
 
 extern "C" size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,

@@ -39,6 +39,9 @@ constexpr int64_t kTypeU4 = 4ll << 8 | 1ll << 50;
 constexpr int64_t kTypeU8B128 = 8ll << 8 | 128ll << 17 | 1ll << 50;
 constexpr int64_t kTypeU8 = 8ll << 8 | 1ll << 50;
 
+// bump the process-wide launch counter (b200q_kernel_launches)
+void note_launch(int n = 1);
+
 int device_sm_count();
 int device_max_smem_optin();
 

@@ -391,6 +391,7 @@ int launch_lookup(const StreamParams& p, int max_ctas, cudaStream_t stream) {
   int grid = (int)(want < by_work ? want : by_work);
   if (grid < 1) grid = 1;
   kernel<<<grid, kStreamThreads, Cfg::kSmemBytes, stream>>>(p);
+  note_launch();
   B200Q_CUDA_OK(cudaGetLastError());
   return B200Q_OK;
 }

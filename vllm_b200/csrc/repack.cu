@@ -194,6 +194,7 @@ int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* o
   permute_cols_kernel<<<blocks, 256, smem, stream>>>(
       static_cast<const uint16_t*>(a), lda, perm, static_cast<uint16_t*>(out), (int)size_m,
       (int)size_k, stage);
+  note_launch();
   B200Q_CUDA_OK(cudaGetLastError());
   return B200Q_OK;
 }
@@ -232,6 +233,7 @@ extern "C" int b200q_gptq_marlin_repack(const uint32_t* b_q_weight, const int32_
       gptq_repack_kernel<8, false><<<grid, kRepackThreads, 0, stream>>>(b_q_weight, perm, out,
                                                                           (int)size_k, (int)size_n);
   }
+  note_launch();
   B200Q_CUDA_OK(cudaGetLastError());
   return B200Q_OK;
 }
@@ -256,6 +258,7 @@ extern "C" int b200q_awq_marlin_repack(const uint32_t* b_q_weight, uint32_t* out
   else
     awq_repack_kernel<8><<<grid, kRepackThreads, 0, stream>>>(b_q_weight, out, (int)size_k,
                                                                (int)size_n);
+  note_launch();
   B200Q_CUDA_OK(cudaGetLastError());
   return B200Q_OK;
 }
