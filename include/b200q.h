@@ -125,6 +125,32 @@ int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q_weight,
                       int64_t size_m, int64_t size_n, int64_t size_k,
                       int64_t num_groups, unsigned flags, b200q_stream_t stream);
 
+/*
+ * b200q_marlin_gemm for callers that cannot allocate device memory (a plugin
+ * running inside another framework's fixed memory plan, code that runs while a
+ * stream is being captured, a process whose device memory belongs to another
+ * component).  Same arguments as b200q_marlin_gemm without scratch /
+ * scratch_bytes: the scratch is a fixed array inside the library, of
+ * b200q_marlin_gemm_noalloc_max_scratch() bytes (16 MiB), which every GPU that
+ * loads the library holds until the process exits.  The call allocates nothing
+ * and calls no allocating routine.
+ *   - Problems whose b200q_marlin_gemm_scratch_bytes(...) exceeds that size are
+ *     rejected with B200Q_ESCRATCH (use b200q_marlin_gemm with your own scratch).
+ *   - The first call on each device resolves the array's device address
+ *     (cudaGetSymbolAddress); make that first call before any stream capture.
+ *   - All calls on a device share the one array: calls that can overlap on the
+ *     GPU (different streams) race on it and must be ordered by the caller.
+ * This entry point has no counterpart in the reference.
+ */
+size_t b200q_marlin_gemm_noalloc_max_scratch(void);
+int b200q_marlin_gemm_noalloc(const void* a, int64_t lda, const uint32_t* b_q_weight,
+                              const void* b_scales, const uint32_t* b_zeros,
+                              const int32_t* g_idx, const int32_t* perm,
+                              const void* b_bias, void* c, int32_t* workspace,
+                              int64_t workspace_len, int64_t b_q_type_id, int a_dtype,
+                              int64_t size_m, int64_t size_n, int64_t size_k,
+                              int64_t num_groups, unsigned flags, b200q_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

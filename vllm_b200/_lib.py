@@ -22,6 +22,8 @@ EXPORTS = (
     "b200q_permute_cols",
     "b200q_marlin_gemm_scratch_bytes",
     "b200q_marlin_gemm",
+    "b200q_marlin_gemm_noalloc_max_scratch",
+    "b200q_marlin_gemm_noalloc",
 )
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4
@@ -67,8 +69,11 @@ def load() -> ctypes.CDLL:
     lib.b200q_marlin_gemm.argtypes = [
         vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, c.c_size_t, vp, i64, i64, i32,
         i64, i64, i64, i64, u32, vp]
-    if hasattr(lib, "b200q_marlin_gemm_noalloc"):
-        lib.b200q_marlin_gemm_noalloc.restype = i32
+    lib.b200q_marlin_gemm_noalloc_max_scratch.restype = c.c_size_t
+    lib.b200q_marlin_gemm_noalloc_max_scratch.argtypes = []
+    lib.b200q_marlin_gemm_noalloc.restype = i32
+    lib.b200q_marlin_gemm_noalloc.argtypes = [
+        vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i64, i64, i64, i64, u32, vp]
     _lib = lib
     return lib
 
