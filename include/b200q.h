@@ -49,6 +49,13 @@ int b200q_version(void);
  * GEMM workspace from this (marlin_utils.py:237-245). */
 int b200q_sm_count(void);
 
+/* Error word of the tensor-core GEMM on the current device: 0, or a code naming
+ * the first hand-off wait that ran into its poll limit (the kernel then drains
+ * and returns instead of hanging).  Synchronises the device.  reset != 0 clears
+ * it.  No counterpart in the reference, whose device-side waits are unbounded
+ * (csrc/quantization/gptq_marlin/marlin_template.h:225-235). */
+int b200q_device_error(int reset);
+
 /* Number of kernels this library has launched in the process so far (all
  * entry points, all threads).  Lets a caller count the launches of a timed
  * region.  No counterpart in the reference. */

@@ -17,6 +17,7 @@ EXPORTS = (
     "b200q_version",
     "b200q_sm_count",
     "b200q_kernel_launches",
+    "b200q_device_error",
     "b200q_gptq_marlin_repack",
     "b200q_awq_marlin_repack",
     "b200q_permute_cols",
@@ -56,6 +57,8 @@ def load() -> ctypes.CDLL:
     lib.b200q_version.restype = i32
     lib.b200q_sm_count.restype = i32
     lib.b200q_kernel_launches.restype = c.c_ulonglong
+    lib.b200q_device_error.restype = i32
+    lib.b200q_device_error.argtypes = [i32]
     lib.b200q_kernel_launches.argtypes = []
     lib.b200q_gptq_marlin_repack.restype = i32
     lib.b200q_gptq_marlin_repack.argtypes = [vp, vp, vp, i64, i64, i32, vp]

@@ -52,6 +52,13 @@ template <typename T, int BITS>
 int dispatch_stream(const StreamParams& p, bool has_zp, int gm, int mb, int ntw, int max_ctas,
                     cudaStream_t stream);
 
+bool tc_gemm_supported(int64_t size_m, int64_t size_n, int64_t size_k, int gm);
+int launch_tc_gemm(const void* a, int64_t lda, const uint32_t* b, const void* scales,
+                   const uint32_t* zeros, const void* bias, void* c, int a_dtype, int bits,
+                   int64_t size_m, int64_t size_n, int64_t size_k, int group_blocks,
+                   int channelwise, cudaStream_t stream);
+int tc_error_flag(bool reset);
+
 int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* out, int64_t size_m,
                         int64_t size_k, cudaStream_t stream);
 
@@ -70,6 +77,16 @@ int grouped_ntw() {
     v = (e && e[0] == '1') ? 1 : 2;
   }
   return v;
+}
+
+// B200Q_DISABLE_TC=1 routes every M through the decode kernels (debugging aid).
+bool tc_path_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200Q_DISABLE_TC");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
 }
 
 inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
@@ -91,6 +108,7 @@ extern "C" const char* b200q_last_error(void) { return g_error; }
 extern "C" int b200q_version(void) { return 100; }
 extern "C" unsigned long long b200q_kernel_launches(void) { return g_launches.load(); }
 extern "C" int b200q_sm_count(void) { return device_sm_count(); }
+extern "C" int b200q_device_error(int reset) { return tc_error_flag(reset != 0); }
 
 extern "C" size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
                                                   int has_act_order) {
@@ -210,7 +228,12 @@ extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q
     lda_used = size_k;
   }
 
-  // ---- launches: chunks of up to 64 rows ---------------------------------------------
+  // ---- prefill regime: tensor-core kernel ----------------------------------------------
+  if (tc_path_enabled() && tc_gemm_supported(size_m, size_n, size_k, gm))
+    return launch_tc_gemm(a_used, lda_used, b_q_weight, b_scales, b_zeros, b_bias, c, a_dtype, bits,
+                          size_m, size_n, size_k, group_blocks, gm == kChannel, stream);
+
+  // ---- decode regime: chunks of up to 64 rows --------------------------------------------
   const int nt = (int)(size_n / 64);
   int64_t max_ctas = workspace_len < kMaxGrid ? workspace_len : kMaxGrid;
   for (int64_t m0 = 0; m0 < size_m; m0 += kMaxRowsPerLaunch) {

@@ -140,6 +140,12 @@ struct Pair<__nv_bfloat16> {
         __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);
   }
+  static __device__ __forceinline__ uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+    __nv_bfloat162 r =
+        __hfma2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b),
+                *reinterpret_cast<__nv_bfloat162*>(&c));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
   static __device__ __forceinline__ float to_float(uint16_t v) {
     return __uint_as_float(static_cast<uint32_t>(v) << 16);
   }

@@ -1,0 +1,560 @@
+// Prefill-regime mixed-precision GEMM on the 5th-generation tensor cores:
+// C[M,N] = A[M,K] * dequant(B) for M > 64, tcgen05.mma with TMEM accumulators.
+//
+// One persistent CTA per SM walks over BM x 128 output tiles (BM = 128 or 256
+// rows of A, m fastest so that CTAs running together share weight tiles).  The
+// k loop advances 64 at a time through a ring of shared-memory stages:
+//
+//   producer warp   TMA (cp.async.bulk.tensor.2d, 128B swizzle, no multicast)
+//                   brings the A tile [BM x 64]; four 1-D bulk copies bring the
+//                   packed weights of the stage (Marlin tiles are contiguous);
+//   4 dequant warps read the packed words, convert them exactly to 16-bit
+//                   (mantissa embedding), subtract the bias or zero-point,
+//                   multiply by the group scale (one 16-bit rounding, the same
+//                   point at which the reference rounds) and store the
+//                   [128 x 64] K-major, 128B-swizzled B operand;
+//   MMA warp        one thread issues tcgen05.mma.kind::f16 (128 x 128 x 16,
+//                   four per stage and accumulator) into TMEM and commits the
+//                   stage back to the producer;
+//   4 epilogue warps tcgen05.ld the finished accumulator, add bias, convert and
+//                   store C while the MMA warp already fills the other TMEM
+//                   buffer.
+//
+// All hand-offs are mbarriers.  Every wait is bounded: after kSpinLimit polls
+// a role records an error code in g_tc_error, stops waiting and lets the
+// kernel drain (TMEM is still freed), so a broken hand-off can not hang the GPU.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_params.cuh"
+
+namespace b200q {
+
+int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* out, int64_t size_m,
+                        int64_t size_k, cudaStream_t stream);
+
+namespace tc {
+
+constexpr int kBN = 128;          // tile columns (two 64-column Marlin tiles)
+constexpr int kBK = 64;           // k per stage: one 128-byte swizzle row of 16-bit values
+constexpr int kDequantWarps = 4;  // warps 0..3
+constexpr int kEpiWarp0 = 4;      // warps 4..7: TMEM lane quadrant = warp % 4
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 320;
+constexpr uint32_t kSpinLimit = 1u << 26;
+
+__device__ int g_tc_error;  // 0 = ok; else (role << 8) | barrier id of the first timed-out wait
+
+struct TcParams {
+  const uint32_t* b;      // Marlin layout
+  const void* scales;     // [G, N] permuted
+  const uint32_t* zeros;  // [G, N/pf] or null
+  const void* bias;       // [N] permuted or null
+  void* c;                // [M, N]
+  int m, n, k;
+  int group_blocks;       // k-tiles (16 rows) per scale group; K/16 when there is one group
+  int channelwise;        // scales use the 32-column "single" permutation
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+// Bounded wait on a phase parity.  Returns false (and records `what`) on time-out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int what) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    // now and then: stop early if another role has already given up
+    if ((spin & 4095u) == 4095u && *reinterpret_cast<volatile int*>(&g_tc_error) != 0) return false;
+  }
+  atomicCAS(&g_tc_error, 0, what);
+  return false;
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::
+          "r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst),
+               "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], 128 x 128 x 16, 16-bit inputs, fp32 accumulate
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on an mbarrier when all MMAs issued so far by this thread have completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::
+                   "r"(bar)
+               : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns of TMEM -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+      "%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B
+// apart, 8-row atoms 1024 B apart (version 1 = sm_100 format).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+
+template <int BM, int BITS>
+struct TcCfg {
+  static constexpr int kABytes = BM * 128;
+  static constexpr int kBBytes = kBN * 128;
+  static constexpr int kTileBytes = 16 * 64 * BITS / 8;    // one packed 16 x 64 weight tile
+  static constexpr int kWBytes = 4 * 2 * kTileBytes;       // 4 k-tiles x 2 column tiles
+  static constexpr int kStageBytes = kABytes + kBBytes + kWBytes;
+  static constexpr int kStages = (220 * 1024) / kStageBytes > 6 ? 6 : (220 * 1024) / kStageBytes;
+  static constexpr int kAccs = BM / 128;                   // 128-row accumulators per tile
+  static constexpr int kTmemCols = 2 * kAccs * kBN;        // double-buffered: 256 or 512
+  static constexpr int kBarBytes = 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+};
+
+// instruction descriptor: fp32 accumulate, A and B K-major, N = 128, M = 128
+template <typename T>
+__device__ __forceinline__ uint32_t make_idesc();
+template <>
+__device__ __forceinline__ uint32_t make_idesc<half>() {
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((kBN >> 3) << 17) | ((128u >> 4) << 24);
+}
+template <>
+__device__ __forceinline__ uint32_t make_idesc<__nv_bfloat16>() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+template <typename T, int BITS, bool HAS_ZP, int BM>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
+  using Cfg = TcCfg<BM, BITS>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = smem_base + S * Cfg::kStageBytes;
+  // barrier ids (8 bytes each)
+  auto full_a = [&](int s) { return bars + 8 * s; };
+  auto full_w = [&](int s) { return bars + 8 * (S + s); };
+  auto full_b = [&](int s) { return bars + 8 * (2 * S + s); };
+  auto empty = [&](int s) { return bars + 8 * (3 * S + s); };
+  auto tmem_full = [&](int b) { return bars + 8 * (4 * S + b); };
+  auto tmem_empty = [&](int b) { return bars + 8 * (4 * S + 2 + b); };
+  const uint32_t tmem_slot = bars + 8 * (4 * S + 4);
+  auto stage_a = [&](int s) { return smem_base + s * Cfg::kStageBytes; };
+  auto stage_b = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kABytes; };
+  auto stage_w = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (p.m + BM - 1) / BM;
+  const int n_tiles = (p.n + kBN - 1) / kBN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int kb_total = p.k / kBK;
+  const int NT = p.n / 64;  // 64-column Marlin tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_a(s), 1);
+      mbar_init(full_w(s), 1);
+      mbar_init(full_b(s), kDequantWarps);
+      mbar_init(empty(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full(b), 1);
+      mbar_init(tmem_empty(b), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == kMmaWarp) tmem_alloc(tmem_slot, Cfg::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == kProducerWarp) {
+    // ================= producer: TMA for A, bulk copies for the packed weights ===========
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int tn = t / m_tiles, tm = t % m_tiles;
+        const int nt0 = tn * 2;
+        const int nt_valid = min(2, NT - nt0);
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!(ok = mbar_wait(empty(s), ph ^ 1, (1 << 8) | 3))) break;
+          mbar_expect_tx(full_a(s), Cfg::kABytes);
+#pragma unroll
+          for (int h = 0; h < Cfg::kAccs; ++h)
+            tma_load_2d(stage_a(s) + h * 128 * 128, &a_map, kb * kBK, tm * BM + h * 128, full_a(s));
+          mbar_expect_tx(full_w(s), 4 * nt_valid * Cfg::kTileBytes);
+#pragma unroll
+          for (int kt = 0; kt < 4; ++kt)
+            bulk_load_1d(stage_w(s) + kt * 2 * Cfg::kTileBytes,
+                         reinterpret_cast<const unsigned char*>(p.b) +
+                             ((size_t)(kb * 4 + kt) * NT + nt0) * Cfg::kTileBytes,
+                         nt_valid * Cfg::kTileBytes, full_w(s));
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ================= MMA issuer ========================================================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc<T>();
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+        const int buf = tile_i & 1;
+        const uint32_t bph = (tile_i >> 1) & 1;
+        if (!(ok = mbar_wait(tmem_empty(buf), bph ^ 1, (2 << 8) | 5))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!(ok = mbar_wait(full_a(s), ph, (2 << 8) | 0))) break;
+          if (!(ok = mbar_wait(full_b(s), ph, (2 << 8) | 2))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int h = 0; h < Cfg::kAccs; ++h) {
+            const uint32_t d = tmem_base + (buf * Cfg::kAccs + h) * kBN;
+            const uint64_t da = smem_desc_sw128(stage_a(s) + h * 128 * 128);
+            const uint64_t db = smem_desc_sw128(stage_b(s));
+#pragma unroll
+            for (int k16 = 0; k16 < kBK / 16; ++k16)
+              umma_f16(d, da + 2 * k16, db + 2 * k16, idesc, (kb | k16) != 0);
+          }
+          umma_commit(empty(s));  // stage reusable once these MMAs have read it
+        }
+        if (ok) umma_commit(tmem_full(buf));
+      }
+    }
+  } else if (warp < kDequantWarps) {
+    // ================= dequant warps: packed codes -> scaled 16-bit B operand ============
+    const int c8 = lane >> 2, q = lane & 3;
+    const uint16_t* __restrict__ SC = static_cast<const uint16_t*>(p.scales);
+    // byte offsets of this lane's two k-positions (k = 16 warp + 2q, +8) inside a 128 B row
+    const uint32_t off_lo = (((2 * warp) ^ c8) << 4) + 4 * q;
+    const uint32_t off_hi = (((2 * warp + 1) ^ c8) << 4) + 4 * q;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int tn = t / m_tiles;
+      const int nt0 = tn * 2;
+      const int nt_valid = min(2, NT - nt0);
+      int cur_g = -1;
+      uint32_t sdup[2][8];   // scale of column c8 + 8 jj, duplicated into both halves
+      uint32_t zdup[2][8];   // zero-point likewise (exact integer in T)
+      (void)zdup;
+      for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1;
+        const int g = p.channelwise ? 0 : (kb * 4 + warp) / p.group_blocks;
+        if (g != cur_g) {
+          cur_g = g;
+          for (int nt = 0; nt < nt_valid; ++nt) {
+            uint32_t sv[4];
+            if (p.channelwise) {
+#pragma unroll
+              for (int jj = 0; jj < 8; jj += 2) {
+                const int n0 = (nt0 + nt) * 64 + c8 + 8 * jj;
+                sv[jj / 2] = (uint32_t)SC[single_perm_pos(n0)] |
+                             ((uint32_t)SC[single_perm_pos(n0 + 8)] << 16);
+              }
+            } else {
+              const uint4 s4 = *reinterpret_cast<const uint4*>(SC + (size_t)g * p.n +
+                                                               (nt0 + nt) * 64 + c8 * 8);
+              sv[0] = s4.x; sv[1] = s4.y; sv[2] = s4.z; sv[3] = s4.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              sdup[nt][2 * i] = dup_lo(sv[i]);
+              sdup[nt][2 * i + 1] = dup_hi(sv[i]);
+            }
+            if (HAS_ZP) {
+              uint32_t zp[4];
+              if (BITS == 4) {
+                dequant4<T, false>(p.zeros[(size_t)g * (p.n / 8) + (nt0 + nt) * 8 + c8], zp);
+              } else {
+                uint32_t t0[2], t1[2];
+                const uint32_t* zr = p.zeros + (size_t)g * (p.n / 4) + (nt0 + nt) * 16 + 2 * c8;
+                dequant8<T, false>(zr[0], t0);
+                dequant8<T, false>(zr[1], t1);
+                zp[0] = t0[0]; zp[1] = t0[1]; zp[2] = t1[0]; zp[3] = t1[1];
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                zdup[nt][2 * i] = dup_lo(zp[i]);
+                zdup[nt][2 * i + 1] = dup_hi(zp[i]);
+              }
+            }
+          }
+        }
+        if (!(ok = mbar_wait(full_w(s), ph, (3 << 8) | 1))) break;
+        const uint32_t wsrc = stage_w(s) + warp * 2 * Cfg::kTileBytes;
+        const uint32_t bdst = stage_b(s);
+        for (int nt = 0; nt < nt_valid; ++nt) {
+          uint32_t w[BITS == 4 ? 4 : 8];
+          if (BITS == 4) {
+            const uint4 w4 = lds128(wsrc + nt * 512 + lane * 16);
+            w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
+          } else {
+            const uint4 w4 = lds128(wsrc + nt * 1024 + lane * 32);
+            const uint4 w5 = lds128(wsrc + nt * 1024 + lane * 32 + 16);
+            w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
+            w[4] = w5.x; w[5] = w5.y; w[6] = w5.z; w[7] = w5.w;
+          }
+#pragma unroll
+          for (int sub = 0; sub < 4; ++sub) {
+            uint32_t f[4];  // (cols c8, k lo), (c8, k hi), (c8 + 8, k lo), (c8 + 8, k hi)
+            if (BITS == 4) {
+              dequant4<T, !HAS_ZP>(w[sub], f);
+            } else {
+              uint32_t t0[2], t1[2];
+              dequant8<T, !HAS_ZP>(w[2 * sub], t0);
+              dequant8<T, !HAS_ZP>(w[2 * sub + 1], t1);
+              f[0] = t0[0]; f[1] = t0[1]; f[2] = t1[0]; f[3] = t1[1];
+            }
+            if (HAS_ZP) {
+              f[0] = Pair<T>::sub(f[0], zdup[nt][2 * sub]);
+              f[1] = Pair<T>::sub(f[1], zdup[nt][2 * sub]);
+              f[2] = Pair<T>::sub(f[2], zdup[nt][2 * sub + 1]);
+              f[3] = Pair<T>::sub(f[3], zdup[nt][2 * sub + 1]);
+            }
+            f[0] = Pair<T>::mul(f[0], sdup[nt][2 * sub]);
+            f[1] = Pair<T>::mul(f[1], sdup[nt][2 * sub]);
+            f[2] = Pair<T>::mul(f[2], sdup[nt][2 * sub + 1]);
+            f[3] = Pair<T>::mul(f[3], sdup[nt][2 * sub + 1]);
+            const uint32_t row = bdst + (nt * 64 + sub * 16 + c8) * 128;
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_lo), "r"(f[0]) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_hi), "r"(f[1]) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_lo), "r"(f[2]) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_hi), "r"(f[3]) : "memory");
+          }
+        }
+        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_b(s));
+      }
+    }
+  } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
+    // ================= epilogue: TMEM -> registers -> C ==================================
+    const int quad = warp & 3;  // TMEM lanes 32 quad .. 32 quad + 31
+    const uint16_t* bias = static_cast<const uint16_t*>(p.bias);
+    uint16_t* C = static_cast<uint16_t*>(p.c);
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+      const int tn = t / m_tiles, tm = t % m_tiles;
+      const int buf = tile_i & 1;
+      const uint32_t bph = (tile_i >> 1) & 1;
+      if (!(ok = mbar_wait(tmem_full(buf), bph, (4 << 8) | 4))) break;
+      tc_fence_after();
+#pragma unroll
+      for (int h = 0; h < Cfg::kAccs; ++h) {
+        const int row = tm * BM + h * 128 + quad * 32 + lane;
+#pragma unroll
+        for (int cb = 0; cb < kBN / 32; ++cb) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (buf * Cfg::kAccs + h) * kBN + cb * 32,
+                    r);
+          tmem_ld_wait();
+          const int n0 = tn * kBN + cb * 32;
+          if (row < p.m && n0 < p.n) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              float v0 = __uint_as_float(r[e]), v1 = __uint_as_float(r[e + 1]);
+              if (bias) {
+                v0 += Pair<T>::to_float(bias[single_perm_pos(n0 + e)]);
+                v1 += Pair<T>::to_float(bias[single_perm_pos(n0 + e + 1)]);
+              }
+              packed[e / 2] =
+                  (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(C + (size_t)row * p.n + n0);
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2],
+                                  packed[4 * v + 3]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty(buf));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+template <typename T, int BITS, bool HAS_ZP, int BM>
+static int launch_one(const CUtensorMap& map, const TcParams& p, cudaStream_t stream) {
+  using Cfg = TcCfg<BM, BITS>;
+  auto kernel = gemm_tc_kernel<T, BITS, HAS_ZP, BM>;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  B200Q_CUDA_OK(cudaGetDevice(&dev));
+  if (!attr_done[dev & 63]) {
+    B200Q_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::kSmemBytes));
+    attr_done[dev & 63] = true;
+  }
+  const int tiles = ((p.m + BM - 1) / BM) * ((p.n + kBN - 1) / kBN);
+  const int sms = device_sm_count();
+  const int grid = tiles < sms ? tiles : sms;
+  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map, p);
+  note_launch();
+  B200Q_CUDA_OK(cudaGetLastError());
+  return B200Q_OK;
+}
+
+template <typename T, int BITS>
+static int launch_bits(const CUtensorMap& map, const TcParams& p, bool has_zp, int bm,
+                       cudaStream_t stream) {
+  if (has_zp)
+    return bm == 128 ? launch_one<T, BITS, true, 128>(map, p, stream)
+                     : launch_one<T, BITS, true, 256>(map, p, stream);
+  return bm == 128 ? launch_one<T, BITS, false, 128>(map, p, stream)
+                   : launch_one<T, BITS, false, 256>(map, p, stream);
+}
+
+}  // namespace tc
+
+// True when the tensor-core kernel can take this problem.
+bool tc_gemm_supported(int64_t size_m, int64_t size_n, int64_t size_k, int gm) {
+  return size_m > 64 && size_k % tc::kBK == 0 && size_n % 64 == 0 && gm != kLookup &&
+         tc::get_encode_fn() != nullptr;
+}
+
+// a: [M, K] 16-bit row-major with row stride lda (already gathered for act-order).
+int launch_tc_gemm(const void* a, int64_t lda, const uint32_t* b, const void* scales,
+                   const uint32_t* zeros, const void* bias, void* c, int a_dtype, int bits,
+                   int64_t size_m, int64_t size_n, int64_t size_k, int group_blocks,
+                   int channelwise, cudaStream_t stream) {
+  CUtensorMap map;
+  const cuuint64_t gdim[2] = {(cuuint64_t)size_k, (cuuint64_t)size_m};
+  const cuuint64_t gstride[1] = {(cuuint64_t)lda * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)tc::kBK, 128};
+  const cuuint32_t estride[2] = {1, 1};
+  CUresult r = tc::get_encode_fn()(
+      &map, a_dtype == B200Q_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+      2, const_cast<void*>(a), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200Q_REQUIRE(r == CUDA_SUCCESS, B200Q_ECUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  tc::TcParams p;
+  p.b = b; p.scales = scales; p.zeros = zeros; p.bias = bias; p.c = c;
+  p.m = (int)size_m; p.n = (int)size_n; p.k = (int)size_k;
+  p.group_blocks = group_blocks; p.channelwise = channelwise;
+  // 256-row tiles once they fill the GPU, else 128-row tiles for more CTAs
+  const int64_t tiles256 = ((size_m + 255) / 256) * ((size_n + 127) / 128);
+  const int bm = (size_m > 128 && tiles256 >= device_sm_count()) ? 256 : 128;
+  const bool has_zp = zeros != nullptr;
+  if (a_dtype == B200Q_F16)
+    return bits == 4 ? tc::launch_bits<half, 4>(map, p, has_zp, bm, stream)
+                     : tc::launch_bits<half, 8>(map, p, has_zp, bm, stream);
+  return bits == 4 ? tc::launch_bits<__nv_bfloat16, 4>(map, p, has_zp, bm, stream)
+                   : tc::launch_bits<__nv_bfloat16, 8>(map, p, has_zp, bm, stream);
+}
+
+int tc_error_flag(bool reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, tc::g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(tc::g_tc_error, &zero, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace b200q
