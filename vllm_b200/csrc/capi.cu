@@ -229,7 +229,7 @@ extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q
   }
 
   // ---- prefill regime: tensor-core kernel ----------------------------------------------
-  if (tc_path_enabled() && tc_gemm_supported(size_m, size_n, size_k, gm))
+  if (tc_path_enabled() && group_blocks >= 2 && tc_gemm_supported(size_m, size_n, size_k, gm))
     return launch_tc_gemm(a_used, lda_used, b_q_weight, b_scales, b_zeros, b_bias, c, a_dtype, bits,
                           size_m, size_n, size_k, group_blocks, gm == kChannel, stream);
 

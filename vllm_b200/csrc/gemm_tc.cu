@@ -1,24 +1,25 @@
 // Prefill-regime mixed-precision GEMM on the 5th-generation tensor cores:
 // C[M,N] = A[M,K] * dequant(B) for M > 64, tcgen05.mma with TMEM accumulators.
 //
-// One persistent CTA per SM walks over BM x 128 output tiles (BM = 128 or 256
-// rows of A, m fastest so that CTAs running together share weight tiles).  The
-// k loop advances 64 at a time through a ring of shared-memory stages:
+// One persistent CTA per SM walks over BM x BN output tiles (BM, BN in {128,
+// 256}; m fastest so that CTAs running together share weight tiles).  The k
+// loop advances 64 at a time through a ring of shared-memory stages:
 //
 //   producer warp   TMA (cp.async.bulk.tensor.2d, 128B swizzle, no multicast)
-//                   brings the A tile [BM x 64]; four 1-D bulk copies bring the
-//                   packed weights of the stage (Marlin tiles are contiguous);
-//   4 dequant warps read the packed words, convert them exactly to 16-bit
+//                   brings the A tile [BM x 64]; 1-D bulk copies bring the packed
+//                   weights of the stage (Marlin tiles are contiguous) and the
+//                   scale / zero-point rows of the groups the stage touches;
+//   8 dequant warps read the packed words, convert them exactly to 16-bit
 //                   (mantissa embedding), subtract the bias or zero-point,
 //                   multiply by the group scale (one 16-bit rounding, the same
 //                   point at which the reference rounds) and store the
-//                   [128 x 64] K-major, 128B-swizzled B operand;
-//   MMA warp        one thread issues tcgen05.mma.kind::f16 (128 x 128 x 16,
-//                   four per stage and accumulator) into TMEM and commits the
-//                   stage back to the producer;
+//                   [BN x 64] K-major, 128B-swizzled B operand;
+//   MMA warp        one thread issues tcgen05.mma.kind::f16 (128 x BN x 16,
+//                   four per stage and 128-row accumulator) into TMEM and
+//                   commits the stage back to the producer;
 //   4 epilogue warps tcgen05.ld the finished accumulator, add bias, convert and
-//                   store C while the MMA warp already fills the other TMEM
-//                   buffer.
+//                   store C; when two accumulator sets fit in TMEM (all but
+//                   256 x 256) the MMA warp meanwhile fills the other one.
 //
 // All hand-offs are mbarriers.  Every wait is bounded: after kSpinLimit polls
 // a role records an error code in g_tc_error, stops waiting and lets the
@@ -35,13 +36,12 @@ int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* o
 
 namespace tc {
 
-constexpr int kBN = 128;          // tile columns (two 64-column Marlin tiles)
 constexpr int kBK = 64;           // k per stage: one 128-byte swizzle row of 16-bit values
-constexpr int kDequantWarps = 4;  // warps 0..3
-constexpr int kEpiWarp0 = 4;      // warps 4..7: TMEM lane quadrant = warp % 4
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kDequantWarps = 8;  // warps 0..7: k-tile = warp % 4, column half = warp / 4
+constexpr int kEpiWarp0 = 8;      // warps 8..11: TMEM lane quadrant = warp % 4
+constexpr int kProducerWarp = 12;
+constexpr int kMmaWarp = 13;
+constexpr int kThreads = 448;
 constexpr uint32_t kSpinLimit = 1u << 26;
 
 __device__ int g_tc_error;  // 0 = ok; else (role << 8) | barrier id of the first timed-out wait
@@ -161,37 +161,45 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
          (2ull << 61);
 }
 
-template <int BM, int BITS>
+template <int BM, int BN, int BITS>
 struct TcCfg {
+  static constexpr int kNT = BN / 64;                      // 64-column Marlin tiles per tile
   static constexpr int kABytes = BM * 128;
-  static constexpr int kBBytes = kBN * 128;
+  static constexpr int kBBytes = BN * 128;
   static constexpr int kTileBytes = 16 * 64 * BITS / 8;    // one packed 16 x 64 weight tile
-  static constexpr int kWBytes = 4 * 2 * kTileBytes;       // 4 k-tiles x 2 column tiles
-  static constexpr int kStageBytes = kABytes + kBBytes + kWBytes;
-  static constexpr int kStages = (220 * 1024) / kStageBytes > 6 ? 6 : (220 * 1024) / kStageBytes;
+  static constexpr int kWBytes = 4 * kNT * kTileBytes;     // 4 k-tiles x kNT column tiles
+  static constexpr int kSRow = BN * 2;                     // one group's scales for the tile
+  static constexpr int kZRow = kNT * 8 * BITS;             // one group's packed zero-points
+  static constexpr int kSOff = kABytes + kBBytes + kWBytes;
+  static constexpr int kZOff = kSOff + 2 * kSRow;          // up to two groups per stage
+  static constexpr int kStageBytes = (kZOff + 2 * kZRow + 1023) / 1024 * 1024;
+  static constexpr int kStagesFit = (222 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 6 ? 6 : kStagesFit;
   static constexpr int kAccs = BM / 128;                   // 128-row accumulators per tile
-  static constexpr int kTmemCols = 2 * kAccs * kBN;        // double-buffered: 256 or 512
+  static constexpr int kBufs = (2 * kAccs * BN <= 512) ? 2 : 1;
+  static constexpr int kTmemCols = (kBufs * kAccs * BN <= 256) ? 256 : 512;
   static constexpr int kBarBytes = 1024;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
 };
 
-// instruction descriptor: fp32 accumulate, A and B K-major, N = 128, M = 128
+// instruction descriptor: fp32 accumulate, A and B K-major, M = 128, N = bn
 template <typename T>
-__device__ __forceinline__ uint32_t make_idesc();
+__device__ __forceinline__ uint32_t make_idesc(int bn);
 template <>
-__device__ __forceinline__ uint32_t make_idesc<half>() {
-  return (1u << 4) | (0u << 7) | (0u << 10) | ((kBN >> 3) << 17) | ((128u >> 4) << 24);
+__device__ __forceinline__ uint32_t make_idesc<half>(int bn) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(bn >> 3) << 17) | ((128u >> 4) << 24);
 }
 template <>
-__device__ __forceinline__ uint32_t make_idesc<__nv_bfloat16>() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((128u >> 4) << 24);
+__device__ __forceinline__ uint32_t make_idesc<__nv_bfloat16>(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-template <typename T, int BITS, bool HAS_ZP, int BM>
+template <typename T, int BITS, bool HAS_ZP, int BM, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
-  using Cfg = TcCfg<BM, BITS>;
+  using Cfg = TcCfg<BM, BN, BITS>;
   constexpr int S = Cfg::kStages;
+  constexpr int NTT = Cfg::kNT;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = smem_base + S * Cfg::kStageBytes;
@@ -206,14 +214,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
   auto stage_a = [&](int s) { return smem_base + s * Cfg::kStageBytes; };
   auto stage_b = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kABytes; };
   auto stage_w = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBBytes; };
+  auto stage_s = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kSOff; };
+  auto stage_z = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kZOff; };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int m_tiles = (p.m + BM - 1) / BM;
-  const int n_tiles = (p.n + kBN - 1) / kBN;
+  const int n_tiles = (p.n + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
   const int kb_total = p.k / kBK;
   const int NT = p.n / 64;  // 64-column Marlin tiles
+  const int gb = p.group_blocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -236,14 +247,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
   asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(tmem_base) : "r"(tmem_slot));
 
   if (warp == kProducerWarp) {
-    // ================= producer: TMA for A, bulk copies for the packed weights ===========
+    // ================= producer: TMA for A, bulk copies for weights / scales / zeros =====
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int tn = t / m_tiles, tm = t % m_tiles;
-        const int nt0 = tn * 2;
-        const int nt_valid = min(2, NT - nt0);
+        const int nt0 = tn * NTT;
+        const int nt_valid = min(NTT, NT - nt0);
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -252,25 +263,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
 #pragma unroll
           for (int h = 0; h < Cfg::kAccs; ++h)
             tma_load_2d(stage_a(s) + h * 128 * 128, &a_map, kb * kBK, tm * BM + h * 128, full_a(s));
-          mbar_expect_tx(full_w(s), 4 * nt_valid * Cfg::kTileBytes);
+          const int g0 = (kb * 4) / gb, g1 = (kb * 4 + 3) / gb;  // at most two groups (gb >= 2)
+          const int ng = g1 - g0 + 1;
+          const uint32_t s_bytes = nt_valid * 128, z_bytes = nt_valid * 8 * BITS;
+          mbar_expect_tx(full_w(s), 4 * nt_valid * Cfg::kTileBytes + ng * s_bytes +
+                                        (HAS_ZP ? ng * z_bytes : 0));
 #pragma unroll
           for (int kt = 0; kt < 4; ++kt)
-            bulk_load_1d(stage_w(s) + kt * 2 * Cfg::kTileBytes,
+            bulk_load_1d(stage_w(s) + kt * NTT * Cfg::kTileBytes,
                          reinterpret_cast<const unsigned char*>(p.b) +
                              ((size_t)(kb * 4 + kt) * NT + nt0) * Cfg::kTileBytes,
                          nt_valid * Cfg::kTileBytes, full_w(s));
+          for (int gi = 0; gi < ng; ++gi) {
+            bulk_load_1d(stage_s(s) + gi * Cfg::kSRow,
+                         static_cast<const uint16_t*>(p.scales) + (size_t)(g0 + gi) * p.n + nt0 * 64,
+                         s_bytes, full_w(s));
+            if (HAS_ZP)
+              bulk_load_1d(stage_z(s) + gi * Cfg::kZRow,
+                           p.zeros + (size_t)(g0 + gi) * (p.n * BITS / 32) + nt0 * (2 * BITS),
+                           z_bytes, full_w(s));
+          }
         }
       }
     }
   } else if (warp == kMmaWarp) {
     // ================= MMA issuer ========================================================
     if (lane == 0) {
-      const uint32_t idesc = make_idesc<T>();
+      const uint32_t idesc = make_idesc<T>(BN);
       uint32_t it = 0, tile_i = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
-        const int buf = tile_i & 1;
-        const uint32_t bph = (tile_i >> 1) & 1;
+        const int buf = Cfg::kBufs == 2 ? (tile_i & 1) : 0;
+        const uint32_t bph = Cfg::kBufs == 2 ? ((tile_i >> 1) & 1) : (tile_i & 1);
         if (!(ok = mbar_wait(tmem_empty(buf), bph ^ 1, (2 << 8) | 5))) break;
         tc_fence_after();
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
@@ -281,7 +305,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
           tc_fence_after();
 #pragma unroll
           for (int h = 0; h < Cfg::kAccs; ++h) {
-            const uint32_t d = tmem_base + (buf * Cfg::kAccs + h) * kBN;
+            const uint32_t d = tmem_base + (buf * Cfg::kAccs + h) * BN;
             const uint64_t da = smem_desc_sw128(stage_a(s) + h * 128 * 128);
             const uint64_t db = smem_desc_sw128(stage_b(s));
 #pragma unroll
@@ -296,104 +320,109 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
   } else if (warp < kDequantWarps) {
     // ================= dequant warps: packed codes -> scaled 16-bit B operand ============
     const int c8 = lane >> 2, q = lane & 3;
-    const uint16_t* __restrict__ SC = static_cast<const uint16_t*>(p.scales);
-    // byte offsets of this lane's two k-positions (k = 16 warp + 2q, +8) inside a 128 B row
-    const uint32_t off_lo = (((2 * warp) ^ c8) << 4) + 4 * q;
-    const uint32_t off_hi = (((2 * warp + 1) ^ c8) << 4) + 4 * q;
+    const int kt = warp & 3;             // k-tile of the stage handled by this warp
+    constexpr int NTW = NTT / 2;         // column tiles per warp
+    const int nt_first = (warp >> 2) * NTW;
+    // byte offsets of this lane's two k-positions (k = 16 kt + 2q, +8) inside a 128 B row
+    const uint32_t off_lo = (((2 * kt) ^ c8) << 4) + 4 * q;
+    const uint32_t off_hi = (((2 * kt + 1) ^ c8) << 4) + 4 * q;
     uint32_t it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const int tn = t / m_tiles;
-      const int nt0 = tn * 2;
-      const int nt_valid = min(2, NT - nt0);
-      int cur_g = -1;
-      uint32_t sdup[2][8];   // scale of column c8 + 8 jj, duplicated into both halves
-      uint32_t zdup[2][8];   // zero-point likewise (exact integer in T)
-      (void)zdup;
+      const int nt0 = tn * NTT;
+      const int nt_valid = min(NTT, NT - nt0);
       for (int kb = 0; kb < kb_total; ++kb, ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1;
-        const int g = p.channelwise ? 0 : (kb * 4 + warp) / p.group_blocks;
-        if (g != cur_g) {
-          cur_g = g;
-          for (int nt = 0; nt < nt_valid; ++nt) {
-            uint32_t sv[4];
-            if (p.channelwise) {
+        if (!(ok = mbar_wait(full_w(s), ph, (3 << 8) | 1))) break;
+        const int slot = (kb * 4 + kt) / gb - (kb * 4) / gb;  // which of the stage's groups
+        const uint32_t wsrc = stage_w(s) + kt * NTT * Cfg::kTileBytes;
+        const uint32_t ssrc = stage_s(s) + slot * Cfg::kSRow;
+        const uint32_t zsrc = stage_z(s) + slot * Cfg::kZRow;
+        const uint32_t bdst = stage_b(s);
 #pragma unroll
-              for (int jj = 0; jj < 8; jj += 2) {
-                const int n0 = (nt0 + nt) * 64 + c8 + 8 * jj;
-                sv[jj / 2] = (uint32_t)SC[single_perm_pos(n0)] |
-                             ((uint32_t)SC[single_perm_pos(n0 + 8)] << 16);
+        for (int i = 0; i < NTW; ++i) {
+          const int nt = nt_first + i;
+          if (nt < nt_valid) {
+            // scale of column c8 + 8 jj duplicated into both halves; zero-point likewise
+            uint32_t sdup[8], zdup[8];
+            (void)zdup;
+            {
+              uint32_t sv[4];
+              if (p.channelwise) {
+                // 32-column permutation: column r of a chunk sits at 8 ((r&7)>>1) + 2 (r>>3) + (r&1)
+#pragma unroll
+                for (int jj = 0; jj < 8; jj += 2) {
+                  const uint32_t pos = (jj >> 2) * 32 + 8 * (c8 >> 1) + 2 * (jj & 3) + (c8 & 1);
+                  uint32_t lo, hi;
+                  asm volatile("ld.shared.u16 %0, [%1];\n" : "=r"(lo) : "r"(ssrc + nt * 128 + pos * 2));
+                  asm volatile("ld.shared.u16 %0, [%1];\n" : "=r"(hi) : "r"(ssrc + nt * 128 + pos * 2 + 4));
+                  sv[jj / 2] = lo | (hi << 16);
+                }
+              } else {
+                const uint4 s4 = lds128(ssrc + nt * 128 + c8 * 16);
+                sv[0] = s4.x; sv[1] = s4.y; sv[2] = s4.z; sv[3] = s4.w;
               }
-            } else {
-              const uint4 s4 = *reinterpret_cast<const uint4*>(SC + (size_t)g * p.n +
-                                                               (nt0 + nt) * 64 + c8 * 8);
-              sv[0] = s4.x; sv[1] = s4.y; sv[2] = s4.z; sv[3] = s4.w;
-            }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              sdup[nt][2 * i] = dup_lo(sv[i]);
-              sdup[nt][2 * i + 1] = dup_hi(sv[i]);
+              for (int j = 0; j < 4; ++j) {
+                sdup[2 * j] = dup_lo(sv[j]);
+                sdup[2 * j + 1] = dup_hi(sv[j]);
+              }
             }
             if (HAS_ZP) {
               uint32_t zp[4];
               if (BITS == 4) {
-                dequant4<T, false>(p.zeros[(size_t)g * (p.n / 8) + (nt0 + nt) * 8 + c8], zp);
+                dequant4<T, false>(lds32(zsrc + nt * 32 + c8 * 4), zp);
               } else {
                 uint32_t t0[2], t1[2];
-                const uint32_t* zr = p.zeros + (size_t)g * (p.n / 4) + (nt0 + nt) * 16 + 2 * c8;
-                dequant8<T, false>(zr[0], t0);
-                dequant8<T, false>(zr[1], t1);
+                dequant8<T, false>(lds32(zsrc + nt * 64 + c8 * 8), t0);
+                dequant8<T, false>(lds32(zsrc + nt * 64 + c8 * 8 + 4), t1);
                 zp[0] = t0[0]; zp[1] = t0[1]; zp[2] = t1[0]; zp[3] = t1[1];
               }
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                zdup[nt][2 * i] = dup_lo(zp[i]);
-                zdup[nt][2 * i + 1] = dup_hi(zp[i]);
+              for (int j = 0; j < 4; ++j) {
+                zdup[2 * j] = dup_lo(zp[j]);
+                zdup[2 * j + 1] = dup_hi(zp[j]);
               }
             }
-          }
-        }
-        if (!(ok = mbar_wait(full_w(s), ph, (3 << 8) | 1))) break;
-        const uint32_t wsrc = stage_w(s) + warp * 2 * Cfg::kTileBytes;
-        const uint32_t bdst = stage_b(s);
-        for (int nt = 0; nt < nt_valid; ++nt) {
-          uint32_t w[BITS == 4 ? 4 : 8];
-          if (BITS == 4) {
-            const uint4 w4 = lds128(wsrc + nt * 512 + lane * 16);
-            w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
-          } else {
-            const uint4 w4 = lds128(wsrc + nt * 1024 + lane * 32);
-            const uint4 w5 = lds128(wsrc + nt * 1024 + lane * 32 + 16);
-            w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
-            w[4] = w5.x; w[5] = w5.y; w[6] = w5.z; w[7] = w5.w;
-          }
-#pragma unroll
-          for (int sub = 0; sub < 4; ++sub) {
-            uint32_t f[4];  // (cols c8, k lo), (c8, k hi), (c8 + 8, k lo), (c8 + 8, k hi)
+            uint32_t w[BITS == 4 ? 4 : 8];
             if (BITS == 4) {
-              dequant4<T, !HAS_ZP>(w[sub], f);
+              const uint4 w4 = lds128(wsrc + nt * 512 + lane * 16);
+              w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
             } else {
-              uint32_t t0[2], t1[2];
-              dequant8<T, !HAS_ZP>(w[2 * sub], t0);
-              dequant8<T, !HAS_ZP>(w[2 * sub + 1], t1);
-              f[0] = t0[0]; f[1] = t0[1]; f[2] = t1[0]; f[3] = t1[1];
+              const uint4 w4 = lds128(wsrc + nt * 1024 + lane * 32);
+              const uint4 w5 = lds128(wsrc + nt * 1024 + lane * 32 + 16);
+              w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
+              w[4] = w5.x; w[5] = w5.y; w[6] = w5.z; w[7] = w5.w;
             }
-            if (HAS_ZP) {
-              f[0] = Pair<T>::sub(f[0], zdup[nt][2 * sub]);
-              f[1] = Pair<T>::sub(f[1], zdup[nt][2 * sub]);
-              f[2] = Pair<T>::sub(f[2], zdup[nt][2 * sub + 1]);
-              f[3] = Pair<T>::sub(f[3], zdup[nt][2 * sub + 1]);
+#pragma unroll
+            for (int sub = 0; sub < 4; ++sub) {
+              uint32_t f[4];  // (cols c8, k lo), (c8, k hi), (c8 + 8, k lo), (c8 + 8, k hi)
+              if (BITS == 4) {
+                dequant4<T, !HAS_ZP>(w[sub], f);
+              } else {
+                uint32_t t0[2], t1[2];
+                dequant8<T, !HAS_ZP>(w[2 * sub], t0);
+                dequant8<T, !HAS_ZP>(w[2 * sub + 1], t1);
+                f[0] = t0[0]; f[1] = t0[1]; f[2] = t1[0]; f[3] = t1[1];
+              }
+              if (HAS_ZP) {
+                f[0] = Pair<T>::sub(f[0], zdup[2 * sub]);
+                f[1] = Pair<T>::sub(f[1], zdup[2 * sub]);
+                f[2] = Pair<T>::sub(f[2], zdup[2 * sub + 1]);
+                f[3] = Pair<T>::sub(f[3], zdup[2 * sub + 1]);
+              }
+              f[0] = Pair<T>::mul(f[0], sdup[2 * sub]);
+              f[1] = Pair<T>::mul(f[1], sdup[2 * sub]);
+              f[2] = Pair<T>::mul(f[2], sdup[2 * sub + 1]);
+              f[3] = Pair<T>::mul(f[3], sdup[2 * sub + 1]);
+              const uint32_t row = bdst + (nt * 64 + sub * 16 + c8) * 128;
+              asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_lo), "r"(f[0]) : "memory");
+              asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_hi), "r"(f[1]) : "memory");
+              asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_lo), "r"(f[2]) : "memory");
+              asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_hi), "r"(f[3]) : "memory");
             }
-            f[0] = Pair<T>::mul(f[0], sdup[nt][2 * sub]);
-            f[1] = Pair<T>::mul(f[1], sdup[nt][2 * sub]);
-            f[2] = Pair<T>::mul(f[2], sdup[nt][2 * sub + 1]);
-            f[3] = Pair<T>::mul(f[3], sdup[nt][2 * sub + 1]);
-            const uint32_t row = bdst + (nt * 64 + sub * 16 + c8) * 128;
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_lo), "r"(f[0]) : "memory");
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_hi), "r"(f[1]) : "memory");
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_lo), "r"(f[2]) : "memory");
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_hi), "r"(f[3]) : "memory");
           }
         }
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core
@@ -410,20 +439,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
       const int tn = t / m_tiles, tm = t % m_tiles;
-      const int buf = tile_i & 1;
-      const uint32_t bph = (tile_i >> 1) & 1;
+      const int buf = Cfg::kBufs == 2 ? (tile_i & 1) : 0;
+      const uint32_t bph = Cfg::kBufs == 2 ? ((tile_i >> 1) & 1) : (tile_i & 1);
       if (!(ok = mbar_wait(tmem_full(buf), bph, (4 << 8) | 4))) break;
       tc_fence_after();
 #pragma unroll
       for (int h = 0; h < Cfg::kAccs; ++h) {
         const int row = tm * BM + h * 128 + quad * 32 + lane;
-#pragma unroll
-        for (int cb = 0; cb < kBN / 32; ++cb) {
+#pragma unroll 1
+        for (int cb = 0; cb < BN / 32; ++cb) {
           uint32_t r[32];
-          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (buf * Cfg::kAccs + h) * kBN + cb * 32,
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (buf * Cfg::kAccs + h) * BN + cb * 32,
                     r);
           tmem_ld_wait();
-          const int n0 = tn * kBN + cb * 32;
+          const int n0 = tn * BN + cb * 32;
           if (row < p.m && n0 < p.n) {
             uint32_t packed[16];
 #pragma unroll
@@ -477,10 +506,10 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-template <typename T, int BITS, bool HAS_ZP, int BM>
+template <typename T, int BITS, bool HAS_ZP, int BM, int BN>
 static int launch_one(const CUtensorMap& map, const TcParams& p, cudaStream_t stream) {
-  using Cfg = TcCfg<BM, BITS>;
-  auto kernel = gemm_tc_kernel<T, BITS, HAS_ZP, BM>;
+  using Cfg = TcCfg<BM, BN, BITS>;
+  auto kernel = gemm_tc_kernel<T, BITS, HAS_ZP, BM, BN>;
   static bool attr_done[64] = {};
   int dev = 0;
   B200Q_CUDA_OK(cudaGetDevice(&dev));
@@ -489,7 +518,7 @@ static int launch_one(const CUtensorMap& map, const TcParams& p, cudaStream_t st
                                        Cfg::kSmemBytes));
     attr_done[dev & 63] = true;
   }
-  const int tiles = ((p.m + BM - 1) / BM) * ((p.n + kBN - 1) / kBN);
+  const int tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
   const int sms = device_sm_count();
   const int grid = tiles < sms ? tiles : sms;
   kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map, p);
@@ -498,14 +527,41 @@ static int launch_one(const CUtensorMap& map, const TcParams& p, cudaStream_t st
   return B200Q_OK;
 }
 
-template <typename T, int BITS>
-static int launch_bits(const CUtensorMap& map, const TcParams& p, bool has_zp, int bm,
+template <typename T, int BITS, bool HAS_ZP>
+static int launch_tile(const CUtensorMap& map, const TcParams& p, int bm, int bn,
                        cudaStream_t stream) {
-  if (has_zp)
-    return bm == 128 ? launch_one<T, BITS, true, 128>(map, p, stream)
-                     : launch_one<T, BITS, true, 256>(map, p, stream);
-  return bm == 128 ? launch_one<T, BITS, false, 128>(map, p, stream)
-                   : launch_one<T, BITS, false, 256>(map, p, stream);
+  if (bm == 128)
+    return bn == 128 ? launch_one<T, BITS, HAS_ZP, 128, 128>(map, p, stream)
+                     : launch_one<T, BITS, HAS_ZP, 128, 256>(map, p, stream);
+  return bn == 128 ? launch_one<T, BITS, HAS_ZP, 256, 128>(map, p, stream)
+                   : launch_one<T, BITS, HAS_ZP, 256, 256>(map, p, stream);
+}
+
+template <typename T, int BITS>
+static int launch_bits(const CUtensorMap& map, const TcParams& p, bool has_zp, int bm, int bn,
+                       cudaStream_t stream) {
+  return has_zp ? launch_tile<T, BITS, true>(map, p, bm, bn, stream)
+                : launch_tile<T, BITS, false>(map, p, bm, bn, stream);
+}
+
+// Tile shape for a problem: the candidate with the least estimated time, where a
+// tile's k-step costs max(MMA cycles, bytes brought in / kBytesPerClk) and the
+// grid runs ceil(tiles / SMs) waves.
+static void choose_tile(int64_t m, int64_t n, int bits, int sms, int* bm_out, int* bn_out) {
+  const double kBytesPerClk = 48.0;
+  double best = 1e300;
+  for (int bm = 128; bm <= 256; bm += 128)
+    for (int bn = 128; bn <= 256; bn += 128) {
+      if (bm == 256 && m <= 128) continue;
+      if (bn == 256 && n <= 128) continue;
+      const int64_t tiles = ((m + bm - 1) / bm) * ((n + bn - 1) / bn);
+      const double waves = (double)((tiles + sms - 1) / sms);
+      const double mma = (bm / 128.0) * (bn / 128.0) * 256.0;
+      const double mem = (bm * 128.0 + (bn / 64) * 4 * (128.0 * bits)) / kBytesPerClk;
+      const double epi = (bm == 256 && bn == 256) ? 64.0 : 0.0;  // single-buffered TMEM: epilogue not hidden
+      const double cost = waves * ((mma > mem ? mma : mem) + epi);
+      if (cost < best) { best = cost; *bm_out = bm; *bn_out = bn; }
+    }
 }
 
 }  // namespace tc
@@ -513,7 +569,7 @@ static int launch_bits(const CUtensorMap& map, const TcParams& p, bool has_zp, i
 // True when the tensor-core kernel can take this problem.
 bool tc_gemm_supported(int64_t size_m, int64_t size_n, int64_t size_k, int gm) {
   return size_m > 64 && size_k % tc::kBK == 0 && size_n % 64 == 0 && gm != kLookup &&
-         tc::get_encode_fn() != nullptr;
+         tc::get_encode_fn() != nullptr;  // group_blocks >= 2 is checked by the caller
 }
 
 // a: [M, K] 16-bit row-major with row stride lda (already gathered for act-order).
@@ -536,15 +592,14 @@ int launch_tc_gemm(const void* a, int64_t lda, const uint32_t* b, const void* sc
   p.b = b; p.scales = scales; p.zeros = zeros; p.bias = bias; p.c = c;
   p.m = (int)size_m; p.n = (int)size_n; p.k = (int)size_k;
   p.group_blocks = group_blocks; p.channelwise = channelwise;
-  // 256-row tiles once they fill the GPU, else 128-row tiles for more CTAs
-  const int64_t tiles256 = ((size_m + 255) / 256) * ((size_n + 127) / 128);
-  const int bm = (size_m > 128 && tiles256 >= device_sm_count()) ? 256 : 128;
+  int bm = 128, bn = 128;
+  tc::choose_tile(size_m, size_n, bits, device_sm_count(), &bm, &bn);
   const bool has_zp = zeros != nullptr;
   if (a_dtype == B200Q_F16)
-    return bits == 4 ? tc::launch_bits<half, 4>(map, p, has_zp, bm, stream)
-                     : tc::launch_bits<half, 8>(map, p, has_zp, bm, stream);
-  return bits == 4 ? tc::launch_bits<__nv_bfloat16, 4>(map, p, has_zp, bm, stream)
-                   : tc::launch_bits<__nv_bfloat16, 8>(map, p, has_zp, bm, stream);
+    return bits == 4 ? tc::launch_bits<half, 4>(map, p, has_zp, bm, bn, stream)
+                     : tc::launch_bits<half, 8>(map, p, has_zp, bm, bn, stream);
+  return bits == 4 ? tc::launch_bits<__nv_bfloat16, 4>(map, p, has_zp, bm, bn, stream)
+                   : tc::launch_bits<__nv_bfloat16, 8>(map, p, has_zp, bm, bn, stream);
 }
 
 int tc_error_flag(bool reset) {
