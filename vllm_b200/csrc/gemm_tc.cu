@@ -9,7 +9,7 @@
 //                   brings the A tile [BM x 64]; 1-D bulk copies bring the packed
 //                   weights of the stage (Marlin tiles are contiguous) and the
 //                   scale / zero-point rows of the groups the stage touches;
-//   8 dequant warps read the packed words, convert them exactly to 16-bit
+//   16 dequant warps (two groups taking alternate stages) read the packed words, convert them exactly to 16-bit
 //                   (mantissa embedding), subtract the bias or zero-point,
 //                   multiply by the group scale (one 16-bit rounding, the same
 //                   point at which the reference rounds) and store the
@@ -26,6 +26,8 @@
 // kernel drain (TMEM is still freed), so a broken hand-off can not hang the GPU.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_params.cuh"
 
@@ -37,11 +39,12 @@ int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* o
 namespace tc {
 
 constexpr int kBK = 64;           // k per stage: one 128-byte swizzle row of 16-bit values
-constexpr int kDequantWarps = 8;  // warps 0..7: k-tile = warp % 4, column half = warp / 4
-constexpr int kEpiWarp0 = 8;      // warps 8..11: TMEM lane quadrant = warp % 4
-constexpr int kProducerWarp = 12;
-constexpr int kMmaWarp = 13;
-constexpr int kThreads = 448;
+constexpr int kDequantGroups = 2;  // groups of 8 dequant warps; group g converts stages it % 2 == g
+constexpr int kDequantWarps = 8 * kDequantGroups;  // in a group: k-tile = warp % 4, column half = warp / 4
+constexpr int kEpiWarp0 = kDequantWarps;           // 4 warps: TMEM lane quadrant = warp % 4
+constexpr int kProducerWarp = kEpiWarp0 + 4;
+constexpr int kMmaWarp = kProducerWarp + 1;
+constexpr int kThreads = 32 * (kMmaWarp + 1);
 constexpr uint32_t kSpinLimit = 1u << 26;
 
 __device__ int g_tc_error;  // 0 = ok; else (role << 8) | barrier id of the first timed-out wait
@@ -230,7 +233,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full_a(s), 1);
       mbar_init(full_w(s), 1);
-      mbar_init(full_b(s), kDequantWarps);
+      mbar_init(full_b(s), 8);
       mbar_init(empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -320,9 +323,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
   } else if (warp < kDequantWarps) {
     // ================= dequant warps: packed codes -> scaled 16-bit B operand ============
     const int c8 = lane >> 2, q = lane & 3;
+    const int dq_group = warp >> 3;      // converts the stages with it % kDequantGroups == dq_group
     const int kt = warp & 3;             // k-tile of the stage handled by this warp
     constexpr int NTW = NTT / 2;         // column tiles per warp
-    const int nt_first = (warp >> 2) * NTW;
+    const int nt_first = ((warp >> 2) & 1) * NTW;
     // byte offsets of this lane's two k-positions (k = 16 kt + 2q, +8) inside a 128 B row
     const uint32_t off_lo = (((2 * kt) ^ c8) << 4) + 4 * q;
     const uint32_t off_hi = (((2 * kt + 1) ^ c8) << 4) + 4 * q;
@@ -333,6 +337,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
       const int nt0 = tn * NTT;
       const int nt_valid = min(NTT, NT - nt0);
       for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        if ((int)(it % kDequantGroups) != dq_group) continue;
         const int s = it % S;
         const uint32_t ph = (it / S) & 1;
         if (!(ok = mbar_wait(full_w(s), ph, (3 << 8) | 1))) break;
@@ -544,24 +549,23 @@ static int launch_bits(const CUtensorMap& map, const TcParams& p, bool has_zp, i
                 : launch_tile<T, BITS, false>(map, p, bm, bn, stream);
 }
 
-// Tile shape for a problem: the candidate with the least estimated time, where a
-// tile's k-step costs max(MMA cycles, bytes brought in / kBytesPerClk) and the
-// grid runs ceil(tiles / SMs) waves.
+// Tile shape for a problem: least estimated time = waves * tile area / efficiency,
+// with the relative efficiencies measured on B200 at M = 4096 (the dequant warps'
+// time per k-step is nearly constant, so tiles with more MMA work per converted
+// column run closer to the tensor-pipe rate).
 static void choose_tile(int64_t m, int64_t n, int bits, int sms, int* bm_out, int* bn_out) {
-  const double kBytesPerClk = 48.0;
+  (void)bits;
+  static const struct { int bm, bn; double eff; } kCand[4] = {
+      {256, 256, 1.00}, {256, 128, 0.72}, {128, 256, 0.65}, {128, 128, 0.50}};
   double best = 1e300;
-  for (int bm = 128; bm <= 256; bm += 128)
-    for (int bn = 128; bn <= 256; bn += 128) {
-      if (bm == 256 && m <= 128) continue;
-      if (bn == 256 && n <= 128) continue;
-      const int64_t tiles = ((m + bm - 1) / bm) * ((n + bn - 1) / bn);
-      const double waves = (double)((tiles + sms - 1) / sms);
-      const double mma = (bm / 128.0) * (bn / 128.0) * 256.0;
-      const double mem = (bm * 128.0 + (bn / 64) * 4 * (128.0 * bits)) / kBytesPerClk;
-      const double epi = (bm == 256 && bn == 256) ? 64.0 : 0.0;  // single-buffered TMEM: epilogue not hidden
-      const double cost = waves * ((mma > mem ? mma : mem) + epi);
-      if (cost < best) { best = cost; *bm_out = bm; *bn_out = bn; }
-    }
+  for (const auto& c : kCand) {
+    if (c.bm == 256 && m <= 128) continue;
+    if (c.bn == 256 && n <= 128) continue;
+    const int64_t tiles = ((m + c.bm - 1) / c.bm) * ((n + c.bn - 1) / c.bn);
+    const double waves = (double)((tiles + sms - 1) / sms);
+    const double cost = waves * c.bm * c.bn / c.eff;
+    if (cost < best) { best = cost; *bm_out = c.bm; *bn_out = c.bn; }
+  }
 }
 
 }  // namespace tc
@@ -594,6 +598,14 @@ int launch_tc_gemm(const void* a, int64_t lda, const uint32_t* b, const void* sc
   p.group_blocks = group_blocks; p.channelwise = channelwise;
   int bm = 128, bn = 128;
   tc::choose_tile(size_m, size_n, bits, device_sm_count(), &bm, &bn);
+  if (const char* e = getenv("B200Q_TC_TILE")) {  // tuning aid: "BMxBN", e.g. 256x256
+    int fm = 0, fn = 0;
+    if (sscanf(e, "%dx%d", &fm, &fn) == 2 && (fm == 128 || fm == 256) && (fn == 128 || fn == 256) &&
+        (fm == 128 || size_m > 128)) {
+      bm = fm;
+      bn = fn;
+    }
+  }
   const bool has_zp = zeros != nullptr;
   if (a_dtype == B200Q_F16)
     return bits == 4 ? tc::launch_bits<half, 4>(map, p, has_zp, bm, bn, stream)
