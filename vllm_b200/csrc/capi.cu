@@ -34,6 +34,15 @@ static void query_device(int dev) {
     g_smem_optin[dev & 63] = v;
 }
 
+bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200Q_NO_PDL");
+    v = (e && e[0] == '1') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 int device_sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;

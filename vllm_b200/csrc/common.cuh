@@ -42,6 +42,9 @@ constexpr int64_t kTypeU8 = 8ll << 8 | 1ll << 50;
 // bump the process-wide launch counter (b200q_kernel_launches)
 void note_launch(int n = 1);
 
+// false when B200Q_NO_PDL=1 (programmatic dependent launch off: debugging aid)
+bool pdl_enabled();
+
 int device_sm_count();
 int device_max_smem_optin();
 

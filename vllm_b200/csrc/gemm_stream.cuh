@@ -224,6 +224,11 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
 #pragma unroll
   for (int i = 0; i < kABlocks; ++i) a_bytes[i] = (i * 16 + fr < p.m) ? 16 : 0;
 
+  // let the next kernel in the stream start its own weight prefetch early
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  bool first_piece = true;
+  if (u_begin >= u_end) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
   for (long long u = u_begin; u < u_end;) {
     const int slice = (int)(u / KT);
     const int kt0 = (int)(u % KT);
@@ -269,18 +274,24 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
     int i_first_left = (GM == kGrouped) ? gb - wb % gb : 0;
     int issued = 0;
 
-    auto issue = [&]() {
+    uint32_t i_stw = ring;  // next stage to fill with weights (runs ahead only in the prologue)
+    auto issue_w = [&]() {
 #pragma unroll
       for (int j = 0; j < NTW; ++j) {
         if (BITS == 4) {
-          cp_async16(i_st + j * 512 + lane * 16, i_w + j * 512);
+          cp_async16(i_stw + j * 512 + lane * 16, i_w + j * 512);
         } else {
           // 16 B chunk ch of a tile belongs to lane ch/2, half ch%2
-          cp_async16(i_st + j * 1024 + (lane & 1) * 512 + (lane >> 1) * 16, i_w + j * 1024);
-          cp_async16(i_st + j * 1024 + (lane & 1) * 512 + (16 + (lane >> 1)) * 16,
+          cp_async16(i_stw + j * 1024 + (lane & 1) * 512 + (lane >> 1) * 16, i_w + j * 1024);
+          cp_async16(i_stw + j * 1024 + (lane & 1) * 512 + (16 + (lane >> 1)) * 16,
                      i_w + j * 1024 + 512);
         }
       }
+      i_w += w_kt_stride;
+      i_stw += Cfg::kStageBytes;
+      if (i_stw == ring_end) i_stw = ring;
+    };
+    auto issue_a = [&]() {
 #pragma unroll
       for (int i = 0; i < kABlocks; ++i)
         cp_async16(i_st + Cfg::kAOff + i * 512 + a_fill_off,
@@ -303,10 +314,13 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
         }
         --i_left;
       }
-      i_w += w_kt_stride;
       i_a += 32;
       i_st += Cfg::kStageBytes;
       if (i_st == ring_end) i_st = ring;
+    };
+    auto issue = [&]() {
+      issue_w();
+      issue_a();
     };
 
     // ---- group end: fold the open group's sums into acc ---------------------------------
@@ -367,13 +381,32 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
       }
     };
 
+    if (first_piece) {
+      // The weights do not depend on the kernel before this one in the stream:
+      // start streaming them, and only then wait for that kernel to finish
+      // (programmatic dependent launch) before touching A, scales' consumers,
+      // scratch or C.  The whole prologue forms one cp.async group.
+      first_piece = false;
+      const int pw = n_steps < D - 1 ? n_steps : D - 1;
 #pragma unroll
-    for (int s = 0; s < D - 1; ++s) {
-      if (issued < n_steps) {
-        issue();
-        ++issued;
+      for (int s = 0; s < D - 1; ++s)
+        if (s < pw) issue_w();
+      asm volatile("griddepcontrol.wait;\n" ::: "memory");
+#pragma unroll
+      for (int s = 0; s < D - 1; ++s)
+        if (s < pw) issue_a();
+      issued = pw;
+#pragma unroll
+      for (int s = 0; s < D - 1; ++s) cp_async_commit();
+    } else {
+#pragma unroll
+      for (int s = 0; s < D - 1; ++s) {
+        if (issued < n_steps) {
+          issue();
+          ++issued;
+        }
+        cp_async_commit();
       }
-      cp_async_commit();
     }
 
     uint32_t c_st = ring;
@@ -667,7 +700,19 @@ int launch_stream(StreamParams p, int max_ctas, cudaStream_t stream) {
   const long long by_work = (total + 15) / 16;  // at least 16 k-tiles per CTA
   int grid = (int)(want < by_work ? want : by_work);
   if (grid < 1) grid = 1;
-  kernel<<<grid, kStreamThreads, Cfg::kSmemBytes, stream>>>(p);
+  // programmatic dependent launch: the kernel may start while its predecessor in
+  // the stream drains; it orders itself with griddepcontrol.wait
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kStreamThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, p));
   note_launch();
   B200Q_CUDA_OK(cudaGetLastError());
   return B200Q_OK;

@@ -160,6 +160,8 @@ __global__ void __launch_bounds__(256)
 permute_cols_kernel(const uint16_t* __restrict__ a, int64_t lda, const int32_t* __restrict__ perm,
                     uint16_t* __restrict__ out, int size_m, int size_k, int stage_in_smem) {
   extern __shared__ __align__(16) uint16_t row_buf[];
+  // the GEMM that follows may start prefetching its weights right away
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   for (int m = blockIdx.x; m < size_m; m += gridDim.x) {
     const uint16_t* src = a + (size_t)m * lda;
     uint16_t* dst = out + (size_t)m * size_k;
