@@ -28,16 +28,16 @@
 //    This is also more accurate than rounding w*s to 16 bits first.
 //
 // Work decomposition.  The weight matrix is cut into column "slices" of NTW
-// 64-column tiles; a slice has KT = K/16 k-tiles, so there are S*KT units of
-// work laid out slice-major.  The grid takes equal contiguous ranges of units
-// ("stripes"), so every CTA streams the same number of bytes whatever the
-// shape.  Inside a CTA the 8 warps split the k-range of the current piece; their
-// partial sums meet in shared memory.  A slice that spans several CTAs is
-// finished by whichever CTA arrives last at the slice's counter: every CTA
-// writes its fp32 partial to scratch, the last one adds all partials in CTA
-// order (bitwise reproducible, no spinning) and writes C.  Counters are
-// returned to zero.
+// 64-column tiles.  A slice is owned by a thread-block cluster of 1, 2, 4 or 8
+// CTAs that split K evenly (enough CTAs to fill the GPU); inside a CTA the 8
+// warps split the CTA's k-range again.  Warp sums meet in shared memory; CTA
+// sums meet through distributed shared memory: every CTA publishes its tile,
+// and after a cluster barrier each CTA adds the ranks' copies of its share of
+// the rows in rank order and stores C.  No global scratch, no atomics, no
+// spinning, and the result is bitwise reproducible.
 #pragma once
+
+#include <cstdlib>
 
 #include "gemm_params.cuh"
 
@@ -173,9 +173,11 @@ struct StreamCfg {
   // reduction buffer: one 8-row block of every warp's accumulators, [row][column]
   static constexpr int kRedStride = 64 * NTW + 4;  // floats; +4 keeps the scalar stores conflict-free
   static constexpr int kRedBytes = kStreamWarps * 8 * kRedStride * 4;
-  static constexpr int kSmemBytes = kRingBytes > kRedBytes ? kRingBytes : kRedBytes;
+  // the CTA's finished tile, published to the cluster after the reduction
+  static constexpr int kXBytes = MT * 8 * 64 * NTW * 4;
+  static constexpr int kSmemBytes =
+      kRingBytes > kRedBytes + kXBytes ? kRingBytes : kRedBytes + kXBytes;
   static constexpr int kEpt = 2 * NTW;  // output elements per thread per 8-row block
-  static constexpr int kSlotFloats = MT * 8 * 64 * NTW;
 };
 
 template <typename T, int BITS, bool HAS_ZP, int GM, int MT, int NTW, int MINB>
@@ -197,14 +199,16 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
   const uint16_t* __restrict__ S = static_cast<const uint16_t*>(p.scales);
   const uint32_t ex = p.c_ex, mlo = p.c_mask_lo, mhi = p.c_mask_hi;
 
-  const long long total = (long long)p.slices * KT;
-  const long long u_begin = total * blockIdx.x / gridDim.x;
-  const long long u_end = total * (blockIdx.x + 1) / gridDim.x;
+  // cluster = the CTAs that share one column slice; rank = which part of K
+  uint32_t ksplit, krank;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(ksplit));
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(krank));
 
   const uint32_t ring = smem_u32(smem) + warp * Cfg::kWarpBytes;
   const uint32_t slots = ring + D * Cfg::kStageBytes;
   float* red = reinterpret_cast<float*>(smem);
-  __shared__ int s_is_last;
+  // this CTA's finished tile, read by the other CTAs of the cluster
+  float* xbuf = reinterpret_cast<float*>(smem + Cfg::kRedBytes);
 
   // ---- lane-constant addressing of the A rows inside a stage -------------------------
   // A is staged as rows of 32 B (16 k-values); 16 B chunk (row r, half h) lives at
@@ -227,13 +231,11 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
   // let the next kernel in the stream start its own weight prefetch early
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   bool first_piece = true;
-  if (u_begin >= u_end) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
-  for (long long u = u_begin; u < u_end;) {
-    const int slice = (int)(u / KT);
-    const int kt0 = (int)(u % KT);
-    const int kt1 = (int)min((long long)KT, kt0 + (u_end - u));
-    u += kt1 - kt0;
+  {
+    const int slice = blockIdx.x / ksplit;
+    const int kt0 = (int)((long long)KT * krank / ksplit);
+    const int kt1 = (int)((long long)KT * (krank + 1) / ksplit);
     const int nt0 = slice * NTW;  // first 64-column tile of the slice
 
     // this warp's contiguous share of [kt0, kt1)
@@ -536,10 +538,6 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
     }
 
     // ---- intra-CTA reduction, one 8-row block at a time ----------------------------
-    const long long s_first_u = (long long)slice * KT;
-    const int first_cta = (int)(((s_first_u + 1) * gridDim.x - 1) / total);
-    const int last_cta = (int)(((s_first_u + KT) * gridDim.x - 1) / total);
-    const bool split = first_cta != last_cta;
 
     float outv[MT][Cfg::kEpt];
     const int o_row = threadIdx.x >> 5;                // 0..7
@@ -574,67 +572,51 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
       }
     }
 
-    // ---- cross-CTA reduction for split slices --------------------------------------
-    auto slot_ptr = [&](int cta, int i) {
-      return p.partials + (size_t)(cta + slice) * Cfg::kSlotFloats + (i * 8 + o_row) * (64 * NTW) +
-             o_col;
-    };
+    // ---- cross-CTA reduction inside the cluster, through distributed shared memory ----
+    // Every CTA publishes its tile in its own shared memory; after a cluster
+    // barrier the rows of the tile are shared out among the CTAs (row % ksplit),
+    // and each sums the ranks' copies in rank order (bitwise reproducible).
     bool do_store = true;
-    if (split) {
+    if (ksplit > 1) {
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
+        float* dst = xbuf + (i * 8 + o_row) * (64 * NTW) + o_col;
         if constexpr (Cfg::kEpt == 4)
-          __stcg(reinterpret_cast<float4*>(slot_ptr(blockIdx.x, i)),
-                 make_float4(outv[i][0], outv[i][1], outv[i][2], outv[i][3]));
+          *reinterpret_cast<float4*>(dst) = make_float4(outv[i][0], outv[i][1], outv[i][2], outv[i][3]);
         else
-          __stcg(reinterpret_cast<float2*>(slot_ptr(blockIdx.x, i)),
-                 make_float2(outv[i][0], outv[i][1]));
+          *reinterpret_cast<float2*>(dst) = make_float2(outv[i][0], outv[i][1]);
       }
-      __syncthreads();  // all of this CTA's partial is written ...
-      if (threadIdx.x == 0) {
-        // ... and released, with the other CTAs' partials acquired, by one gpu-scope RMW
-        int prev;
-        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;\n"
-                     : "=r"(prev)
-                     : "l"(p.counters + first_cta)
-                     : "memory");
-        s_is_last = (prev == last_cta - first_cta);
-      }
-      __syncthreads();
-      do_store = s_is_last != 0;
-      if (do_store) {
+      asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+      do_store = false;
 #pragma unroll
-        for (int i = 0; i < MT; ++i)
+      for (int i = 0; i < MT; ++i) {
+        const int row = i * 8 + o_row;
+        if ((uint32_t)row % ksplit == krank) {
+          do_store = true;
 #pragma unroll
           for (int e = 0; e < Cfg::kEpt; ++e) outv[i][e] = 0.f;
-        // fixed summation order (CTA order); loads of 4 partials are in flight at a time
-        constexpr int kBatch = 4;
-        for (int cta = first_cta; cta <= last_cta; cta += kBatch) {
-          float v[kBatch][MT][Cfg::kEpt];
-#pragma unroll
-          for (int t = 0; t < kBatch; ++t) {
-            const int src_cta = min(cta + t, last_cta);
-#pragma unroll
-            for (int i = 0; i < MT; ++i) {
-              if constexpr (Cfg::kEpt == 4) {
-                const float4 x = __ldcg(reinterpret_cast<const float4*>(slot_ptr(src_cta, i)));
-                v[t][i][0] = x.x; v[t][i][1] = x.y; v[t][i][2] = x.z; v[t][i][3] = x.w;
-              } else {
-                const float2 x = __ldcg(reinterpret_cast<const float2*>(slot_ptr(src_cta, i)));
-                v[t][i][0] = x.x; v[t][i][1] = x.y;
-              }
+          const uint32_t local = smem_u32(xbuf + row * (64 * NTW) + o_col);
+          for (uint32_t r = 0; r < ksplit; ++r) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local), "r"(r));
+            if constexpr (Cfg::kEpt == 4) {
+              float4 v;
+              asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+                           : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                           : "r"(remote)
+                           : "memory");
+              outv[i][0] += v.x; outv[i][1] += v.y; outv[i][2] += v.z; outv[i][3] += v.w;
+            } else {
+              float2 v;
+              asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];\n"
+                           : "=f"(v.x), "=f"(v.y)
+                           : "r"(remote)
+                           : "memory");
+              outv[i][0] += v.x; outv[i][1] += v.y;
             }
           }
-#pragma unroll
-          for (int t = 0; t < kBatch; ++t)
-            if (cta + t <= last_cta) {
-#pragma unroll
-              for (int i = 0; i < MT; ++i)
-#pragma unroll
-                for (int e = 0; e < Cfg::kEpt; ++e) outv[i][e] += v[t][i][e];
-            }
         }
-        if (threadIdx.x == 0) p.counters[first_cta] = 0;
       }
     }
 
@@ -653,7 +635,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         const int row = i * 8 + o_row;
-        if (row < p.m) {
+        if (row < p.m && (ksplit == 1 || (uint32_t)row % ksplit == krank)) {
           uint32_t packed[Cfg::kEpt / 2];
 #pragma unroll
           for (int e = 0; e < Cfg::kEpt; e += 2) {
@@ -670,7 +652,11 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
         }
       }
     }
-    __syncthreads();  // reduction buffer is reused as the ring of the next piece
+    // no CTA may exit while others still read its shared memory
+    if (ksplit > 1) {
+      asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    }
   }
 }
 
@@ -694,12 +680,17 @@ int launch_stream(StreamParams p, int max_ctas, cudaStream_t stream) {
   p.c_ex = E::kEx;
   p.c_mask_lo = E::kMaskLo;
   p.c_mask_hi = E::kMaskHi;
-  const long long total = (long long)p.slices * p.kt_total;
-  long long want = (long long)device_sm_count() * kMinBlocks;
-  if (want > max_ctas) want = max_ctas;
-  const long long by_work = (total + 15) / 16;  // at least 16 k-tiles per CTA
-  int grid = (int)(want < by_work ? want : by_work);
-  if (grid < 1) grid = 1;
+  // K is split over a cluster of 1, 2, 4 or 8 CTAs: enough to fill the GPU, at
+  // least 8 k-tiles (one per warp) each
+  const int target = device_sm_count() * kMinBlocks;
+  int ksplit = 1;
+  while (ksplit < 8 && p.slices * ksplit * 2 <= target && p.kt_total / (ksplit * 2) >= 8) ksplit *= 2;
+  if (const char* e = getenv("B200Q_STREAM_KSPLIT")) {  // tuning aid
+    const int v = atoi(e);
+    if (v == 1 || v == 2 || v == 4 || v == 8) ksplit = v;
+  }
+  (void)max_ctas;
+  const int grid = p.slices * ksplit;
   // programmatic dependent launch: the kernel may start while its predecessor in
   // the stream drains; it orders itself with griddepcontrol.wait
   cudaLaunchConfig_t cfg = {};
@@ -707,11 +698,15 @@ int launch_stream(StreamParams p, int max_ctas, cudaStream_t stream) {
   cfg.blockDim = dim3(kStreamThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = ksplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, p));
   note_launch();
   B200Q_CUDA_OK(cudaGetLastError());
