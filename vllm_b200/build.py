@@ -54,6 +54,7 @@ def _digest() -> str:
             with open(path, "rb") as f:
                 h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(os.environ.get("B200Q_EXTRA_NVCC_FLAGS", "").encode())
     return h.hexdigest()
 
 
@@ -68,6 +69,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(os.path.dirname(LIB), exist_ok=True)
     nvcc = _nvcc()
     flags = NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
+    flags = flags + os.environ.get("B200Q_EXTRA_NVCC_FLAGS", "").split()
 
     def compile_one(unit):
         src, obj, defs = unit

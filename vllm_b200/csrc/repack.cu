@@ -180,11 +180,40 @@ permute_cols_kernel(const uint16_t* __restrict__ a, int64_t lda, const int32_t* 
   }
 }
 
+// Few rows (decode): one thread per 8 output elements, many blocks per row, so
+// that the gather is spread over the whole GPU; the reads hit L2.
+__global__ void __launch_bounds__(256)
+permute_cols_small_kernel(const uint16_t* __restrict__ a, int64_t lda,
+                          const int32_t* __restrict__ perm, uint16_t* __restrict__ out, int size_k) {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  const int m = blockIdx.y;
+  const int k0 = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (k0 >= size_k) return;
+  const uint16_t* src = a + (size_t)m * lda;
+  const int4 p0 = *reinterpret_cast<const int4*>(perm + k0);
+  const int4 p1 = *reinterpret_cast<const int4*>(perm + k0 + 4);
+  uint4 v;
+  v.x = (uint32_t)src[p0.x] | ((uint32_t)src[p0.y] << 16);
+  v.y = (uint32_t)src[p0.z] | ((uint32_t)src[p0.w] << 16);
+  v.z = (uint32_t)src[p1.x] | ((uint32_t)src[p1.y] << 16);
+  v.w = (uint32_t)src[p1.z] | ((uint32_t)src[p1.w] << 16);
+  *reinterpret_cast<uint4*>(out + (size_t)m * size_k + k0) = v;
+}
+
 }  // namespace
 
 int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* out, int64_t size_m,
                         int64_t size_k, cudaStream_t stream) {
   if (size_m == 0 || size_k == 0) return B200Q_OK;
+  if (size_m <= 64 && size_k % 8 == 0 && (reinterpret_cast<uintptr_t>(perm) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    dim3 grid((unsigned)((size_k / 8 + 255) / 256), (unsigned)size_m);
+    permute_cols_small_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(a), lda, perm,
+                                                        static_cast<uint16_t*>(out), (int)size_k);
+    note_launch();
+    B200Q_CUDA_OK(cudaGetLastError());
+    return B200Q_OK;
+  }
   const size_t row_bytes = (size_t)size_k * 2;
   const bool aligned = (lda % 8 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15) == 0);
   int stage = aligned && row_bytes <= (size_t)device_max_smem_optin() - 1024;
