@@ -1,0 +1,70 @@
+"""Tensor-parallel group state and the row-parallel all-reduce.
+
+One process per GPU; the group is a ``torch.distributed`` process group (NCCL
+over NVLink / NVSwitch on GPUs, gloo in CPU tests).  Mirrors the call chain
+``tensor_model_parallel_all_reduce`` -> ``GroupCoordinator.all_reduce`` of the
+reference (vllm/distributed/communication_op.py:12-14,
+vllm/distributed/parallel_state.py:452-479): out-of-place semantics, a no-op
+for a group of one.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+_TP_GROUP = None
+_TP_RANK = 0
+_TP_SIZE = 1
+
+
+def initialize_model_parallel(tensor_model_parallel_size: int | None = None, group=None) -> None:
+    """Use the default (or given) process group as the TP group.  TP ranks are
+    the innermost dimension of the rank layout, as in
+    vllm/distributed/parallel_state.py:1262-1275; only TP is modelled here."""
+    global _TP_GROUP, _TP_RANK, _TP_SIZE
+    if not dist.is_initialized():
+        _TP_GROUP, _TP_RANK, _TP_SIZE = None, 0, 1
+        return
+    _TP_GROUP = group if group is not None else dist.group.WORLD
+    _TP_SIZE = dist.get_world_size(_TP_GROUP)
+    _TP_RANK = dist.get_rank(_TP_GROUP)
+    if tensor_model_parallel_size is not None and tensor_model_parallel_size != _TP_SIZE:
+        raise ValueError(f"tensor_model_parallel_size = {tensor_model_parallel_size} but the "
+                         f"process group has {_TP_SIZE} ranks")
+
+
+def destroy_model_parallel() -> None:
+    global _TP_GROUP, _TP_RANK, _TP_SIZE
+    _TP_GROUP, _TP_RANK, _TP_SIZE = None, 0, 1
+
+
+def get_tensor_model_parallel_world_size() -> int:
+    return _TP_SIZE
+
+
+def get_tensor_model_parallel_rank() -> int:
+    return _TP_RANK
+
+
+def tensor_model_parallel_all_reduce(input_: torch.Tensor) -> torch.Tensor:
+    """SUM all-reduce over the TP group; returns a new tensor (the reference's op
+    is out-of-place, parallel_state.py:117-126)."""
+    if _TP_SIZE == 1:
+        return input_
+    out = input_.clone()
+    dist.all_reduce(out, op=dist.ReduceOp.SUM, group=_TP_GROUP)
+    return out
+
+
+def tensor_model_parallel_all_gather(input_: torch.Tensor, dim: int = -1) -> torch.Tensor:
+    if _TP_SIZE == 1:
+        return input_
+    parts = [torch.empty_like(input_) for _ in range(_TP_SIZE)]
+    dist.all_gather(parts, input_.contiguous(), group=_TP_GROUP)
+    return torch.cat(parts, dim=dim)
+
+
+def divide(numerator: int, denominator: int) -> int:
+    if numerator % denominator != 0:
+        raise ValueError(f"{numerator} is not divisible by {denominator}")
+    return numerator // denominator
