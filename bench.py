@@ -331,13 +331,15 @@ def run_ours(args, world, rank, local_rank):
     if dist is not None:
         dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
     ms2 = ms2.tolist()
-    if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
-    report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks)
+    if rank == 0:
+        report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks)
     if dist is not None:
-        dist.destroy_process_group()
+        # CUDA graphs that captured NCCL kernels are still alive: tearing the communicator down
+        # under them can block, so leave together and let process exit release everything
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks):
