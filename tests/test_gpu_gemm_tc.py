@@ -97,3 +97,30 @@ def test_tc_gemm_full_size_linearity(env):
     w = mo.dequantize(w_codes, s_lin, "bfloat16", bias=8, group_size=128)
     ref = mo.gemm_ref(a1[:48].float().cpu().numpy(), w)
     _check(y1[:48, :64].cpu().numpy(), ref, "corner vs oracle")
+
+
+def test_tc_gemm_many_tiles_per_cta(env):
+    """M = 32768: ~100 tiles per CTA and an activation matrix larger than L2, so
+    the producer is the slow role and stage barriers complete late — the regime in
+    which a hand-off that skips barrier phases goes wrong.  Sampled rows must agree
+    with the decode-regime kernel run on those rows alone."""
+    torch, G, ops, mu, lib = env
+    from vllm_b200.scalar_type import scalar_types
+    M, K, N = 32768, 4096, 2048
+    dev = "cuda"
+    gen = torch.Generator(device=dev).manual_seed(11)
+    q = torch.randint(-2**31, 2**31 - 1, (K // 16, N * 2), dtype=torch.int32, device=dev, generator=gen)
+    s = (torch.rand((K // 128, N), device=dev, generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
+    a = torch.randn((M, K), device=dev, dtype=torch.bfloat16, generator=gen)
+    ws = mu.marlin_make_workspace_new(torch.device(dev))
+    e = torch.empty(0, dtype=torch.int32, device=dev)
+    f = lambda x: ops.gptq_marlin_gemm(x, None, q, None, s, None, e, e, e, ws, scalar_types.uint4b8,
+                                       x.shape[0], N, K, True, False, True, False)
+    for _ in range(2):
+        big = f(a).float()
+        torch.cuda.synchronize()
+        assert lib.b200q_device_error(1) == 0, "a hand-off wait timed out"
+        scale = big.abs().max().item()
+        for r0 in (0, 5000, 16384, 32768 - 16):
+            small = f(a[r0:r0 + 16].contiguous()).float()
+            assert (small - big[r0:r0 + 16]).abs().max().item() <= 2e-2 * scale, r0

@@ -9,7 +9,7 @@
 //                   brings the A tile [BM x 64]; 1-D bulk copies bring the packed
 //                   weights of the stage (Marlin tiles are contiguous) and the
 //                   scale / zero-point rows of the groups the stage touches;
-//   16 dequant warps (two groups taking alternate stages) read the packed words, convert them exactly to 16-bit
+//   16 dequant warps (each a quarter of the columns of one k-tile) read the packed words, convert them exactly to 16-bit
 //                   (mantissa embedding), subtract the bias or zero-point,
 //                   multiply by the group scale (one 16-bit rounding, the same
 //                   point at which the reference rounds) and store the
@@ -39,15 +39,16 @@ int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* o
 namespace tc {
 
 constexpr int kBK = 64;           // k per stage: one 128-byte swizzle row of 16-bit values
-constexpr int kDequantGroups = 2;  // groups of 8 dequant warps; group g converts stages it % 2 == g
-constexpr int kDequantWarps = 8 * kDequantGroups;  // in a group: k-tile = warp % 4, column half = warp / 4
+constexpr int kDequantWarps = 16;  // k-tile of the stage = warp % 4, column quarter = warp / 4
 constexpr int kEpiWarp0 = kDequantWarps;           // 4 warps: TMEM lane quadrant = warp % 4
 constexpr int kProducerWarp = kEpiWarp0 + 4;
 constexpr int kMmaWarp = kProducerWarp + 1;
 constexpr int kThreads = 32 * (kMmaWarp + 1);
 constexpr uint32_t kSpinLimit = 1u << 26;
 
-__device__ int g_tc_error;  // 0 = ok; else (role << 8) | barrier id of the first timed-out wait
+// 0 = ok; else (role << 8) | barrier id of the first wait that ever timed out (sticky, for the
+// host to read).  Roles of the same CTA tell each other to stop through a shared-memory flag.
+__device__ int g_tc_error;
 
 struct TcParams {
   const uint32_t* b;      // Marlin layout
@@ -72,7 +73,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
                : "memory");
 }
 // Bounded wait on a phase parity.  Returns false (and records `what`) on time-out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int what) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int what,
+                                          volatile int* cta_abort) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     uint32_t done;
     asm volatile(
@@ -83,9 +85,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int wha
         : "r"(bar), "r"(parity)
         : "memory");
     if (done) return true;
-    // now and then: stop early if another role has already given up
-    if ((spin & 4095u) == 4095u && *reinterpret_cast<volatile int*>(&g_tc_error) != 0) return false;
+    // now and then: stop early if another role of this CTA has already given up
+    if ((spin & 1023u) == 1023u && *cta_abort != 0) return false;
   }
+  *cta_abort = 1;
   atomicCAS(&g_tc_error, 0, what);
   return false;
 }
@@ -220,6 +223,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
   auto stage_s = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kSOff; };
   auto stage_z = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kZOff; };
 
+  __shared__ int s_abort;
+  volatile int* cta_abort = &s_abort;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int m_tiles = (p.m + BM - 1) / BM;
@@ -230,10 +235,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
   const int gb = p.group_blocks;
 
   if (threadIdx.x == 0) {
+    s_abort = 0;
     for (int s = 0; s < S; ++s) {
       mbar_init(full_a(s), 1);
       mbar_init(full_w(s), 1);
-      mbar_init(full_b(s), 8);
+      mbar_init(full_b(s), kDequantWarps);
       mbar_init(empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -261,7 +267,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!(ok = mbar_wait(empty(s), ph ^ 1, (1 << 8) | 3))) break;
+          if (!(ok = mbar_wait(empty(s), ph ^ 1, (1 << 8) | 3, cta_abort))) break;
           mbar_expect_tx(full_a(s), Cfg::kABytes);
 #pragma unroll
           for (int h = 0; h < Cfg::kAccs; ++h)
@@ -298,13 +304,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
         const int buf = Cfg::kBufs == 2 ? (tile_i & 1) : 0;
         const uint32_t bph = Cfg::kBufs == 2 ? ((tile_i >> 1) & 1) : (tile_i & 1);
-        if (!(ok = mbar_wait(tmem_empty(buf), bph ^ 1, (2 << 8) | 5))) break;
+        if (!(ok = mbar_wait(tmem_empty(buf), bph ^ 1, (2 << 8) | 5, cta_abort))) break;
         tc_fence_after();
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!(ok = mbar_wait(full_a(s), ph, (2 << 8) | 0))) break;
-          if (!(ok = mbar_wait(full_b(s), ph, (2 << 8) | 2))) break;
+          if (!(ok = mbar_wait(full_a(s), ph, (2 << 8) | 0, cta_abort))) break;
+          if (!(ok = mbar_wait(full_b(s), ph, (2 << 8) | 2, cta_abort))) break;
           tc_fence_after();
 #pragma unroll
           for (int h = 0; h < Cfg::kAccs; ++h) {
@@ -323,10 +329,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
   } else if (warp < kDequantWarps) {
     // ================= dequant warps: packed codes -> scaled 16-bit B operand ============
     const int c8 = lane >> 2, q = lane & 3;
-    const int dq_group = warp >> 3;      // converts the stages with it % kDequantGroups == dq_group
     const int kt = warp & 3;             // k-tile of the stage handled by this warp
-    constexpr int NTW = NTT / 2;         // column tiles per warp
-    const int nt_first = ((warp >> 2) & 1) * NTW;
+    const int quarter = warp >> 2;       // which quarter of the tile's columns
+    // BN = 256: one 64-column tile, all four 16-column sub-tiles; BN = 128: half a tile
+    constexpr int kSubs = (BN == 256) ? 4 : 2;
+    const int nt = (BN == 256) ? quarter : (quarter >> 1);
+    const int sub0 = (BN == 256) ? 0 : 2 * (quarter & 1);
     // byte offsets of this lane's two k-positions (k = 16 kt + 2q, +8) inside a 128 B row
     const uint32_t off_lo = (((2 * kt) ^ c8) << 4) + 4 * q;
     const uint32_t off_hi = (((2 * kt + 1) ^ c8) << 4) + 4 * q;
@@ -337,97 +345,96 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
       const int nt0 = tn * NTT;
       const int nt_valid = min(NTT, NT - nt0);
       for (int kb = 0; kb < kb_total; ++kb, ++it) {
-        if ((int)(it % kDequantGroups) != dq_group) continue;
         const int s = it % S;
         const uint32_t ph = (it / S) & 1;
-        if (!(ok = mbar_wait(full_w(s), ph, (3 << 8) | 1))) break;
+        if (!(ok = mbar_wait(full_w(s), ph, (3 << 8) | 1, cta_abort))) break;
         const int slot = (kb * 4 + kt) / gb - (kb * 4) / gb;  // which of the stage's groups
         const uint32_t wsrc = stage_w(s) + kt * NTT * Cfg::kTileBytes;
         const uint32_t ssrc = stage_s(s) + slot * Cfg::kSRow;
         const uint32_t zsrc = stage_z(s) + slot * Cfg::kZRow;
         const uint32_t bdst = stage_b(s);
+        if (nt < nt_valid) {
+          // packed words of this lane for sub-tiles sub0 .. sub0 + kSubs - 1
+          uint32_t wv[kSubs * (BITS == 4 ? 1 : 2)];
+          if (BITS == 4) {
+            if (kSubs == 4) {
+              const uint4 w4 = lds128(wsrc + nt * 512 + lane * 16);
+              wv[0] = w4.x; wv[1] = w4.y; wv[2] = w4.z; wv[3] = w4.w;
+            } else {
+              wv[0] = lds32(wsrc + nt * 512 + lane * 16 + sub0 * 4);
+              wv[1] = lds32(wsrc + nt * 512 + lane * 16 + sub0 * 4 + 4);
+            }
+          } else {
 #pragma unroll
-        for (int i = 0; i < NTW; ++i) {
-          const int nt = nt_first + i;
-          if (nt < nt_valid) {
-            // scale of column c8 + 8 jj duplicated into both halves; zero-point likewise
-            uint32_t sdup[8], zdup[8];
-            (void)zdup;
-            {
-              uint32_t sv[4];
-              if (p.channelwise) {
-                // 32-column permutation: column r of a chunk sits at 8 ((r&7)>>1) + 2 (r>>3) + (r&1)
+            for (int v = 0; v < kSubs / 2; ++v) {
+              const uint4 w4 = lds128(wsrc + nt * 1024 + lane * 32 + sub0 * 8 + v * 16);
+              wv[4 * v] = w4.x; wv[4 * v + 1] = w4.y; wv[4 * v + 2] = w4.z; wv[4 * v + 3] = w4.w;
+            }
+          }
+          uint32_t zw[2] = {0, 0};  // zero-point words of (group, tile, c8)
+          if (HAS_ZP) {
+            if (BITS == 4) {
+              zw[0] = lds32(zsrc + nt * 32 + c8 * 4);
+            } else {
+              zw[0] = lds32(zsrc + nt * 64 + c8 * 8);
+              zw[1] = lds32(zsrc + nt * 64 + c8 * 8 + 4);
+            }
+          }
 #pragma unroll
-                for (int jj = 0; jj < 8; jj += 2) {
-                  const uint32_t pos = (jj >> 2) * 32 + 8 * (c8 >> 1) + 2 * (jj & 3) + (c8 & 1);
-                  uint32_t lo, hi;
-                  asm volatile("ld.shared.u16 %0, [%1];\n" : "=r"(lo) : "r"(ssrc + nt * 128 + pos * 2));
-                  asm volatile("ld.shared.u16 %0, [%1];\n" : "=r"(hi) : "r"(ssrc + nt * 128 + pos * 2 + 4));
-                  sv[jj / 2] = lo | (hi << 16);
-                }
-              } else {
-                const uint4 s4 = lds128(ssrc + nt * 128 + c8 * 16);
-                sv[0] = s4.x; sv[1] = s4.y; sv[2] = s4.z; sv[3] = s4.w;
-              }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                sdup[2 * j] = dup_lo(sv[j]);
-                sdup[2 * j + 1] = dup_hi(sv[j]);
-              }
+          for (int si = 0; si < kSubs; ++si) {
+            const int sub = sub0 + si;
+            // scales of columns c8 + 16 sub (low half) and + 8 (high half)
+            uint32_t sv;
+            if (p.channelwise) {
+              // 32-column permutation: column r of a chunk sits at 8 ((r&7)>>1) + 2 (r>>3) + (r&1)
+              const int jj = 2 * sub;
+              const uint32_t pos = (jj >> 2) * 32 + 8 * (c8 >> 1) + 2 * (jj & 3) + (c8 & 1);
+              uint32_t lo, hi;
+              asm volatile("ld.shared.u16 %0, [%1];\n" : "=r"(lo) : "r"(ssrc + nt * 128 + pos * 2));
+              asm volatile("ld.shared.u16 %0, [%1];\n" : "=r"(hi) : "r"(ssrc + nt * 128 + pos * 2 + 4));
+              sv = lo | (hi << 16);
+            } else {
+              sv = lds32(ssrc + nt * 128 + c8 * 16 + sub * 4);
+            }
+            const uint32_t s_lo = dup_lo(sv), s_hi = dup_hi(sv);
+            uint32_t f[4];  // (cols c8, k lo), (c8, k hi), (c8 + 8, k lo), (c8 + 8, k hi)
+            if (BITS == 4) {
+              dequant4<T, !HAS_ZP>(wv[si], f);
+            } else {
+              uint32_t t0[2], t1[2];
+              dequant8<T, !HAS_ZP>(wv[2 * si], t0);
+              dequant8<T, !HAS_ZP>(wv[2 * si + 1], t1);
+              f[0] = t0[0]; f[1] = t0[1]; f[2] = t1[0]; f[3] = t1[1];
             }
             if (HAS_ZP) {
-              uint32_t zp[4];
+              // zero-points of the same two columns as exact integers in T
+              uint32_t zpair;
               if (BITS == 4) {
-                dequant4<T, false>(lds32(zsrc + nt * 32 + c8 * 4), zp);
+                // nibbles `sub` and `sub + 4` of the word
+                uint32_t z4[4];
+                dequant4<T, false>(zw[0] >> (4 * sub), z4);
+                zpair = z4[0];
               } else {
-                uint32_t t0[2], t1[2];
-                dequant8<T, false>(lds32(zsrc + nt * 64 + c8 * 8), t0);
-                dequant8<T, false>(lds32(zsrc + nt * 64 + c8 * 8 + 4), t1);
-                zp[0] = t0[0]; zp[1] = t0[1]; zp[2] = t1[0]; zp[3] = t1[1];
+                // word sub / 2, bytes (0, 2) for even sub, (1, 3) for odd
+                uint32_t z8[2];
+                dequant8<T, false>((sub & 2) ? zw[1] : zw[0], z8);
+                zpair = (sub & 1) ? z8[1] : z8[0];
               }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                zdup[2 * j] = dup_lo(zp[j]);
-                zdup[2 * j + 1] = dup_hi(zp[j]);
-              }
+              const uint32_t z_lo = dup_lo(zpair), z_hi = dup_hi(zpair);
+              f[0] = Pair<T>::sub(f[0], z_lo);
+              f[1] = Pair<T>::sub(f[1], z_lo);
+              f[2] = Pair<T>::sub(f[2], z_hi);
+              f[3] = Pair<T>::sub(f[3], z_hi);
             }
-            uint32_t w[BITS == 4 ? 4 : 8];
-            if (BITS == 4) {
-              const uint4 w4 = lds128(wsrc + nt * 512 + lane * 16);
-              w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
-            } else {
-              const uint4 w4 = lds128(wsrc + nt * 1024 + lane * 32);
-              const uint4 w5 = lds128(wsrc + nt * 1024 + lane * 32 + 16);
-              w[0] = w4.x; w[1] = w4.y; w[2] = w4.z; w[3] = w4.w;
-              w[4] = w5.x; w[5] = w5.y; w[6] = w5.z; w[7] = w5.w;
-            }
-#pragma unroll
-            for (int sub = 0; sub < 4; ++sub) {
-              uint32_t f[4];  // (cols c8, k lo), (c8, k hi), (c8 + 8, k lo), (c8 + 8, k hi)
-              if (BITS == 4) {
-                dequant4<T, !HAS_ZP>(w[sub], f);
-              } else {
-                uint32_t t0[2], t1[2];
-                dequant8<T, !HAS_ZP>(w[2 * sub], t0);
-                dequant8<T, !HAS_ZP>(w[2 * sub + 1], t1);
-                f[0] = t0[0]; f[1] = t0[1]; f[2] = t1[0]; f[3] = t1[1];
-              }
-              if (HAS_ZP) {
-                f[0] = Pair<T>::sub(f[0], zdup[2 * sub]);
-                f[1] = Pair<T>::sub(f[1], zdup[2 * sub]);
-                f[2] = Pair<T>::sub(f[2], zdup[2 * sub + 1]);
-                f[3] = Pair<T>::sub(f[3], zdup[2 * sub + 1]);
-              }
-              f[0] = Pair<T>::mul(f[0], sdup[2 * sub]);
-              f[1] = Pair<T>::mul(f[1], sdup[2 * sub]);
-              f[2] = Pair<T>::mul(f[2], sdup[2 * sub + 1]);
-              f[3] = Pair<T>::mul(f[3], sdup[2 * sub + 1]);
-              const uint32_t row = bdst + (nt * 64 + sub * 16 + c8) * 128;
-              asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_lo), "r"(f[0]) : "memory");
-              asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_hi), "r"(f[1]) : "memory");
-              asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_lo), "r"(f[2]) : "memory");
-              asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_hi), "r"(f[3]) : "memory");
-            }
+            f[0] = Pair<T>::mul(f[0], s_lo);
+            f[1] = Pair<T>::mul(f[1], s_lo);
+            f[2] = Pair<T>::mul(f[2], s_hi);
+            f[3] = Pair<T>::mul(f[3], s_hi);
+            const uint32_t row = bdst + (nt * 64 + sub * 16 + c8) * 128;
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_lo), "r"(f[0]) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_hi), "r"(f[1]) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_lo), "r"(f[2]) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_hi), "r"(f[3]) : "memory");
           }
         }
         fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core
@@ -446,7 +453,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
       const int tn = t / m_tiles, tm = t % m_tiles;
       const int buf = Cfg::kBufs == 2 ? (tile_i & 1) : 0;
       const uint32_t bph = Cfg::kBufs == 2 ? ((tile_i >> 1) & 1) : (tile_i & 1);
-      if (!(ok = mbar_wait(tmem_full(buf), bph, (4 << 8) | 4))) break;
+      if (!(ok = mbar_wait(tmem_full(buf), bph, (4 << 8) | 4, cta_abort))) break;
       tc_fence_after();
 #pragma unroll
       for (int h = 0; h < Cfg::kAccs; ++h) {

@@ -1,0 +1,201 @@
+"""Minimal Llama-architecture decoder whose every projection runs through the
+quantized linear layers of this package — the harness for the end-to-end decode
+measurement (random-init Llama-3-8B shape, GPTQ uint4b8 g128).
+
+Only what the measurement needs is here: RMSNorm, RoPE, grouped-query attention
+over a static KV cache (torch SDPA), SiLU-gated MLP, greedy sampling; the layer
+order and the four projections per block follow the reference's model
+(vllm/model_executor/models/llama.py:73-347).  Embedding and lm_head stay 16-bit
+and replicated (the reference quantizes lm_head only when the checkpoint says
+so, gptq_marlin.py:198).  Attention, norms and sampling use stock torch ops: they
+are outside the hot path this package replaces.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from .linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
+from .quantization import GPTQMarlinConfig
+
+
+@dataclass
+class LlamaConfig:
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    vocab_size: int = 128256
+    rope_theta: float = 500000.0
+    rms_eps: float = 1e-5
+
+
+def _fill_random_gptq(layer, gen) -> None:
+    """Seeded random codes and scales in checkpoint format, then the regular
+    load-time transform (device repack, scale permutation)."""
+    q = layer.qweight
+    q.data.copy_(torch.randint(-2**31, 2**31 - 1, q.shape, dtype=torch.int32, device=q.device,
+                               generator=gen))
+    s = layer.scales
+    s.data.copy_((torch.rand(s.shape, device=s.device, generator=gen) * 0.018 + 0.002).to(s.dtype))
+    layer.process_weights_after_loading()
+
+
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    v = x.float()
+    v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    return (v * w.float()).to(x.dtype)
+
+
+class DecoderLayer(torch.nn.Module):
+    def __init__(self, cfg: LlamaConfig, qc, dtype, device, gen, tp_rank, tp_size):
+        super().__init__()
+        kw = dict(quant_config=qc, params_dtype=dtype, device=device, tp_rank=tp_rank, tp_size=tp_size)
+        h = cfg.hidden_size
+        self.cfg = cfg
+        self.qkv_proj = QKVParallelLinear(h, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads, **kw)
+        self.o_proj = RowParallelLinear(cfg.num_heads * cfg.head_dim, h, **kw)
+        self.gate_up_proj = MergedColumnParallelLinear(h, [cfg.intermediate_size] * 2, **kw)
+        self.down_proj = RowParallelLinear(cfg.intermediate_size, h, **kw)
+        for lin in (self.qkv_proj, self.o_proj, self.gate_up_proj, self.down_proj):
+            _fill_random_gptq(lin, gen)
+        self.input_norm = torch.nn.Parameter(torch.ones(h, dtype=dtype, device=device), False)
+        self.post_norm = torch.nn.Parameter(torch.ones(h, dtype=dtype, device=device), False)
+        self.n_q = self.qkv_proj.num_heads
+        self.n_kv = self.qkv_proj.num_kv_heads
+
+    def forward(self, x, cos, sin, k_cache, v_cache, pos_index, attn_mask, prefill_len):
+        """x: [B, T, H].  prefill (prefill_len = T > 0): causal attention inside the prompt, KV
+        written to [0, T).  decode (T == 1): KV written at pos_index, attention over the cache
+        under attn_mask [1, 1, 1, S]."""
+        cfg = self.cfg
+        B, T, _ = x.shape
+        h = rms_norm(x, self.input_norm, cfg.rms_eps)
+        qkv = self.qkv_proj(h.view(B * T, -1)).view(B, T, -1)
+        q, k, v = qkv.split([self.n_q * cfg.head_dim, self.n_kv * cfg.head_dim,
+                             self.n_kv * cfg.head_dim], dim=-1)
+        q = q.view(B, T, self.n_q, cfg.head_dim).transpose(1, 2)
+        k = k.view(B, T, self.n_kv, cfg.head_dim).transpose(1, 2)
+        v = v.view(B, T, self.n_kv, cfg.head_dim).transpose(1, 2)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        if prefill_len:
+            k_cache[:, :, :T].copy_(k)
+            v_cache[:, :, :T].copy_(v)
+            attn = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        else:
+            k_cache.index_copy_(2, pos_index, k)
+            v_cache.index_copy_(2, pos_index, v)
+            attn = F.scaled_dot_product_attention(q, k_cache, v_cache, attn_mask=attn_mask,
+                                                  enable_gqa=True)
+        attn = attn.transpose(1, 2).reshape(B * T, -1)
+        x = x + self.o_proj(attn).view(B, T, -1)
+        h = rms_norm(x, self.post_norm, cfg.rms_eps)
+        gu = self.gate_up_proj(h.view(B * T, -1))
+        gate, up = gu.chunk(2, dim=-1)
+        x = x + self.down_proj(F.silu(gate) * up).view(B, T, -1)
+        return x
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotate-half RoPE; cos / sin: [T, head_dim / 2] for the positions of x's T axis."""
+    x1, x2 = x.float().chunk(2, dim=-1)
+    c, s = cos[None, None], sin[None, None]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
+class LlamaDecoder(torch.nn.Module):
+    def __init__(self, cfg: LlamaConfig, max_seq: int, batch: int, dtype=torch.bfloat16,
+                 device="cuda", seed: int = 0, tp_rank: int = 0, tp_size: int = 1):
+        super().__init__()
+        self.cfg, self.max_seq, self.batch = cfg, max_seq, batch
+        gen = torch.Generator(device=device).manual_seed(seed)       # same weights on every rank
+        gen_shard = torch.Generator(device=device).manual_seed(seed * 1000 + 17 + tp_rank)
+        qc = GPTQMarlinConfig(4, 128, desc_act=False)
+        self.embed = (torch.randn(cfg.vocab_size, cfg.hidden_size, device=device, generator=gen)
+                      * 0.02).to(dtype)
+        self.lm_head = (torch.randn(cfg.vocab_size, cfg.hidden_size, device=device, generator=gen)
+                        * 0.02).to(dtype)
+        self.final_norm = torch.ones(cfg.hidden_size, dtype=dtype, device=device)
+        self.layers = torch.nn.ModuleList(
+            DecoderLayer(cfg, qc, dtype, device, gen_shard, tp_rank, tp_size)
+            for _ in range(cfg.num_layers))
+        n_kv = self.layers[0].n_kv
+        self.k_cache = [torch.zeros(batch, n_kv, max_seq, cfg.head_dim, dtype=dtype, device=device)
+                        for _ in range(cfg.num_layers)]
+        self.v_cache = [torch.zeros_like(k) for k in self.k_cache]
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device).float()
+                                        / cfg.head_dim))
+        ang = torch.arange(max_seq, device=device).float()[:, None] * inv[None]
+        self.cos, self.sin = ang.cos(), ang.sin()
+
+    @torch.no_grad()
+    def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens [B, T] -> next token ids [B]."""
+        B, T = tokens.shape
+        x = self.embed[tokens]
+        for i, layer in enumerate(self.layers):
+            x = layer(x, self.cos[:T], self.sin[:T], self.k_cache[i], self.v_cache[i], None, None, T)
+        x = rms_norm(x[:, -1], self.final_norm, self.cfg.rms_eps)
+        return (x @ self.lm_head.t()).argmax(-1)
+
+    @torch.no_grad()
+    def decode_step(self, tokens: torch.Tensor, pos_index: torch.Tensor,
+                    attn_mask: torch.Tensor) -> torch.Tensor:
+        """One token per sequence.  tokens [B]; pos_index int64 [1] (cache slot to write);
+        attn_mask bool [1, 1, 1, max_seq] with the valid cache slots set."""
+        x = self.embed[tokens][:, None]
+        cos, sin = self.cos.index_select(0, pos_index), self.sin.index_select(0, pos_index)
+        for i, layer in enumerate(self.layers):
+            x = layer(x, cos, sin, self.k_cache[i], self.v_cache[i], pos_index, attn_mask, 0)
+        x = rms_norm(x[:, 0], self.final_norm, self.cfg.rms_eps)
+        return (x @ self.lm_head.t()).argmax(-1)
+
+
+@torch.no_grad()
+def generate(model: LlamaDecoder, prompts: torch.Tensor, new_tokens: int, use_graph: bool = True):
+    """Greedy decode.  Returns (tokens [B, new_tokens], prefill_ms, decode_ms), timed with CUDA
+    events; the decode loop replays one captured CUDA graph per step."""
+    dev = prompts.device
+    B, T = prompts.shape
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    out = torch.empty(B, new_tokens, dtype=torch.long, device=dev)
+    cur = torch.empty(B, dtype=torch.long, device=dev)
+    pos = torch.zeros(1, dtype=torch.long, device=dev)
+    mask = torch.zeros(1, 1, 1, model.max_seq, dtype=torch.bool, device=dev)
+    e[0].record()
+    cur.copy_(model.prefill(prompts))
+    out[:, 0] = cur
+    e[1].record()
+    mask[..., :T] = True
+    graph, nxt = None, None
+    if use_graph:
+        pos.fill_(T)
+        mask[..., T] = True
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            nxt = model.decode_step(cur, pos, mask)       # warm-up outside capture
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            nxt = model.decode_step(cur, pos, mask)
+        mask[..., T] = False
+        torch.cuda.synchronize()
+    e[2].record()
+    for i in range(1, new_tokens):
+        p = T + i - 1                                      # slot of the token fed in this step
+        pos.fill_(p)
+        mask[..., p] = True
+        if graph is not None:
+            graph.replay()
+        else:
+            nxt = model.decode_step(cur, pos, mask)
+        cur.copy_(nxt)
+        out[:, i] = cur
+    e[3].record()
+    torch.cuda.synchronize()
+    return out, e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])
