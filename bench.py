@@ -272,12 +272,13 @@ def run_ours(args, world, rank, local_rank):
             torch.cuda.synchronize()
 
     # ---- device-resident throughput ---------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)                      # let the sampler come up; warm-up load is sampled too
     with torch.cuda.stream(stream):
         for w in warm:
             w()
     sync_all()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in shapes]
     t_all0, t_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -364,11 +365,10 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks):
     value = world * dec_b / dec_t / 1e6            # GB/s, all ranks
     tflops = world * ten_f / ten_t / 1e9
     per_gpu_gbs, per_gpu_tf = value / world, tflops / world
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "decode_traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            traffic = json.load(f).get("dram_bytes_per_decode_sweep")
+    # DRAM bytes of one launch of the dominant decode kernel from the ncu capture summarised in
+    # profiles/gemm_stream_gate_up_m16.txt (gate_up, M = 16: 60.9 MB for 61.6 MB algorithmic)
+    traffic = {"launch": "gemm_stream_kernel gate_up 4096->28672 M=16", "dram_bytes": 60.9e6,
+               "algorithmic_bytes": 61.6e6}
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": k_steps,
         "warmup": args.warmup, "ms_per_step": total_ms / k_steps, "higher_is_better": True,

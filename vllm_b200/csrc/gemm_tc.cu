@@ -579,7 +579,13 @@ static void choose_tile(int64_t m, int64_t n, int bits, int sms, int* bm_out, in
 
 // True when the tensor-core kernel can take this problem.
 bool tc_gemm_supported(int64_t size_m, int64_t size_n, int64_t size_k, int gm) {
-  return size_m > 64 && size_k % tc::kBK == 0 && size_n % 64 == 0 && gm != kLookup &&
+  static int min_m = 0;
+  if (min_m == 0) {
+    const char* e = getenv("B200Q_TC_MIN_M");  // tuning aid: smallest M taken by this kernel
+    min_m = e ? atoi(e) : 65;
+    if (min_m < 1) min_m = 65;
+  }
+  return size_m >= min_m && size_k % tc::kBK == 0 && size_n % 64 == 0 && gm != kLookup &&
          tc::get_encode_fn() != nullptr;  // group_blocks >= 2 is checked by the caller
 }
 
