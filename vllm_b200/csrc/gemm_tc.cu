@@ -44,7 +44,8 @@ constexpr int kEpiWarp0 = kDequantWarps;           // 4 warps: TMEM lane quadran
 constexpr int kProducerWarp = kEpiWarp0 + 4;
 constexpr int kMmaWarp = kProducerWarp + 1;
 constexpr int kThreads = 32 * (kMmaWarp + 1);
-constexpr uint32_t kSpinLimit = 1u << 26;
+constexpr uint32_t kSpinLimit = 1u << 24;   // polls; each poll may sleep up to kSuspendNs
+constexpr uint32_t kSuspendNs = 1000;       // try_wait suspend-time hint: pollers leave the issue slots alone
 
 // 0 = ok; else (role << 8) | barrier id of the first wait that ever timed out (sticky, for the
 // host to read).  Roles of the same CTA tell each other to stop through a shared-memory flag.
@@ -73,18 +74,22 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
                : "memory");
 }
 // Bounded wait on a phase parity.  Returns false (and records `what`) on time-out.
+// SLEEP_NS > 0: back off between polls, so that roles with long waits (epilogue, producer) do
+// not take issue slots from the dequant warps.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int what,
                                           volatile int* cta_abort) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kSuspendNs)
         : "memory");
     if (done) return true;
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     // now and then: stop early if another role of this CTA has already given up
     if ((spin & 1023u) == 1023u && *cta_abort != 0) return false;
   }
@@ -174,6 +179,10 @@ struct TcCfg {
   static constexpr int kBBytes = BN * 128;
   static constexpr int kTileBytes = 16 * 64 * BITS / 8;    // one packed 16 x 64 weight tile
   static constexpr int kWBytes = 4 * kNT * kTileBytes;     // 4 k-tiles x kNT column tiles
+  // the weights of a stage arrive as 2-D copies of at most 256 8-byte elements per row
+  static constexpr int kCopyTiles = (kNT * kTileBytes / 8 <= 256) ? kNT : 256 * 8 / kTileBytes;
+  static constexpr int kCopies = kNT / kCopyTiles;
+  static constexpr int kCopyRowBytes = kCopyTiles * kTileBytes;
   static constexpr int kSRow = BN * 2;                     // one group's scales for the tile
   static constexpr int kZRow = kNT * 8 * BITS;             // one group's packed zero-points
   static constexpr int kSOff = kABytes + kBBytes + kWBytes;
@@ -202,7 +211,8 @@ __device__ __forceinline__ uint32_t make_idesc<__nv_bfloat16>(int bn) {
 
 template <typename T, int BITS, bool HAS_ZP, int BM, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
+               const TcParams p) {
   using Cfg = TcCfg<BM, BN, BITS>;
   constexpr int S = Cfg::kStages;
   constexpr int NTT = Cfg::kNT;
@@ -259,30 +269,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
     // ================= producer: TMA for A, bulk copies for weights / scales / zeros =====
     if (lane == 0) {
       uint32_t it = 0;
+      int st_i = 0;
+      uint32_t st_ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int tn = t / m_tiles, tm = t % m_tiles;
         const int nt0 = tn * NTT;
         const int nt_valid = min(NTT, NT - nt0);
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
+          const int s = st_i;
+          const uint32_t ph = st_ph;
+          if (++st_i == S) { st_i = 0; st_ph ^= 1; }
           if (!(ok = mbar_wait(empty(s), ph ^ 1, (1 << 8) | 3, cta_abort))) break;
           mbar_expect_tx(full_a(s), Cfg::kABytes);
 #pragma unroll
           for (int h = 0; h < Cfg::kAccs; ++h)
             tma_load_2d(stage_a(s) + h * 128 * 128, &a_map, kb * kBK, tm * BM + h * 128, full_a(s));
-          const int g0 = (kb * 4) / gb, g1 = (kb * 4 + 3) / gb;  // at most two groups (gb >= 2)
+          // at most two groups per stage (gb >= 2); one when a group spans whole stages
+          const int g0 = (kb * 4) / gb, g1 = (gb & 3) == 0 ? g0 : (kb * 4 + 3) / gb;
           const int ng = g1 - g0 + 1;
           const uint32_t s_bytes = nt_valid * 128, z_bytes = nt_valid * 8 * BITS;
-          mbar_expect_tx(full_w(s), 4 * nt_valid * Cfg::kTileBytes + ng * s_bytes +
-                                        (HAS_ZP ? ng * z_bytes : 0));
+          // packed weights: one 2-D copy of 4 k-tile rows x (NTT tiles of 8-byte elements);
+          // columns past N are zero-filled and still counted in the transaction bytes
+          mbar_expect_tx(full_w(s), Cfg::kWBytes + ng * s_bytes + (HAS_ZP ? ng * z_bytes : 0));
 #pragma unroll
-          for (int kt = 0; kt < 4; ++kt)
-            bulk_load_1d(stage_w(s) + kt * NTT * Cfg::kTileBytes,
-                         reinterpret_cast<const unsigned char*>(p.b) +
-                             ((size_t)(kb * 4 + kt) * NT + nt0) * Cfg::kTileBytes,
-                         nt_valid * Cfg::kTileBytes, full_w(s));
+          for (int c = 0; c < Cfg::kCopies; ++c)
+            tma_load_2d(stage_w(s) + c * 4 * Cfg::kCopyRowBytes, &b_map,
+                        (nt0 + c * Cfg::kCopyTiles) * (Cfg::kTileBytes / 8), kb * 4, full_w(s));
           for (int gi = 0; gi < ng; ++gi) {
             bulk_load_1d(stage_s(s) + gi * Cfg::kSRow,
                          static_cast<const uint16_t*>(p.scales) + (size_t)(g0 + gi) * p.n + nt0 * 64,
@@ -300,6 +313,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc<T>(BN);
       uint32_t it = 0, tile_i = 0;
+      int st_i = 0;
+      uint32_t st_ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
         const int buf = Cfg::kBufs == 2 ? (tile_i & 1) : 0;
@@ -307,8 +322,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
         if (!(ok = mbar_wait(tmem_empty(buf), bph ^ 1, (2 << 8) | 5, cta_abort))) break;
         tc_fence_after();
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1;
+          const int s = st_i;
+          const uint32_t ph = st_ph;
+          if (++st_i == S) { st_i = 0; st_ph ^= 1; }
           if (!(ok = mbar_wait(full_a(s), ph, (2 << 8) | 0, cta_abort))) break;
           if (!(ok = mbar_wait(full_b(s), ph, (2 << 8) | 2, cta_abort))) break;
           tc_fence_after();
@@ -329,6 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
   } else if (warp < kDequantWarps) {
     // ================= dequant warps: packed codes -> scaled 16-bit B operand ============
     const int c8 = lane >> 2, q = lane & 3;
+    const bool gb_mult4 = (gb & 3) == 0;
     const int kt = warp & 3;             // k-tile of the stage handled by this warp
     const int quarter = warp >> 2;       // which quarter of the tile's columns
     // BN = 256: one 64-column tile, all four 16-column sub-tiles; BN = 128: half a tile
@@ -338,36 +355,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
     // byte offsets of this lane's two k-positions (k = 16 kt + 2q, +8) inside a 128 B row
     const uint32_t off_lo = (((2 * kt) ^ c8) << 4) + 4 * q;
     const uint32_t off_hi = (((2 * kt + 1) ^ c8) << 4) + 4 * q;
+    // stage-relative addresses of everything this lane touches
+    // weights of the stage: [copy][k-tile][tile within the copy]
+    const uint32_t w_rel = Cfg::kABytes + Cfg::kBBytes + (nt / Cfg::kCopyTiles) * 4 * Cfg::kCopyRowBytes +
+                           kt * Cfg::kCopyRowBytes + (nt % Cfg::kCopyTiles) * Cfg::kTileBytes;
+    uint32_t row_rel[kSubs];
+#pragma unroll
+    for (int si = 0; si < kSubs; ++si)
+      row_rel[si] = Cfg::kABytes + (nt * 64 + (sub0 + si) * 16 + c8) * 128;
+    uint32_t sbase = smem_base;  // base of the current stage
+    // The proxy fence that publishes the converted operand is slow compared with the
+    // conversion of one stage; with a ring of four or more stages two stages share one fence.
+    constexpr bool kPairStages = S >= 4;
+    int pending = -1;  // stage converted but not yet published
     uint32_t it = 0;
+    int st_i = 0;
+    uint32_t st_ph = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const int tn = t / m_tiles;
       const int nt0 = tn * NTT;
       const int nt_valid = min(NTT, NT - nt0);
       for (int kb = 0; kb < kb_total; ++kb, ++it) {
-        const int s = it % S;
-        const uint32_t ph = (it / S) & 1;
+        const int s = st_i;
+        const uint32_t ph = st_ph;
+        if (++st_i == S) { st_i = 0; st_ph ^= 1; }
         if (!(ok = mbar_wait(full_w(s), ph, (3 << 8) | 1, cta_abort))) break;
-        const int slot = (kb * 4 + kt) / gb - (kb * 4) / gb;  // which of the stage's groups
-        const uint32_t wsrc = stage_w(s) + kt * NTT * Cfg::kTileBytes;
-        const uint32_t ssrc = stage_s(s) + slot * Cfg::kSRow;
-        const uint32_t zsrc = stage_z(s) + slot * Cfg::kZRow;
-        const uint32_t bdst = stage_b(s);
+        // which of the stage's (at most two) groups: always the first when a group spans whole stages
+        const int slot = gb_mult4 ? 0 : (kb * 4 + kt) / gb - (kb * 4) / gb;
+        const uint32_t wsrc = sbase + w_rel;
+        const uint32_t ssrc = sbase + Cfg::kSOff + slot * Cfg::kSRow;
+        const uint32_t zsrc = sbase + Cfg::kZOff + slot * Cfg::kZRow;
+        const uint32_t brow = sbase;
+        sbase = (s + 1 == S) ? smem_base : sbase + Cfg::kStageBytes;
         if (nt < nt_valid) {
           // packed words of this lane for sub-tiles sub0 .. sub0 + kSubs - 1
           uint32_t wv[kSubs * (BITS == 4 ? 1 : 2)];
           if (BITS == 4) {
             if (kSubs == 4) {
-              const uint4 w4 = lds128(wsrc + nt * 512 + lane * 16);
+              const uint4 w4 = lds128(wsrc + lane * 16);
               wv[0] = w4.x; wv[1] = w4.y; wv[2] = w4.z; wv[3] = w4.w;
             } else {
-              wv[0] = lds32(wsrc + nt * 512 + lane * 16 + sub0 * 4);
-              wv[1] = lds32(wsrc + nt * 512 + lane * 16 + sub0 * 4 + 4);
+              wv[0] = lds32(wsrc + lane * 16 + sub0 * 4);
+              wv[1] = lds32(wsrc + lane * 16 + sub0 * 4 + 4);
             }
           } else {
 #pragma unroll
             for (int v = 0; v < kSubs / 2; ++v) {
-              const uint4 w4 = lds128(wsrc + nt * 1024 + lane * 32 + sub0 * 8 + v * 16);
+              const uint4 w4 = lds128(wsrc + lane * 32 + sub0 * 8 + v * 16);
               wv[4 * v] = w4.x; wv[4 * v + 1] = w4.y; wv[4 * v + 2] = w4.z; wv[4 * v + 3] = w4.w;
             }
           }
@@ -430,17 +465,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const TcParams p) {
             f[1] = Pair<T>::mul(f[1], s_lo);
             f[2] = Pair<T>::mul(f[2], s_hi);
             f[3] = Pair<T>::mul(f[3], s_hi);
-            const uint32_t row = bdst + (nt * 64 + sub * 16 + c8) * 128;
+            const uint32_t row = brow + row_rel[si];
             asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_lo), "r"(f[0]) : "memory");
             asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_hi), "r"(f[1]) : "memory");
             asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_lo), "r"(f[2]) : "memory");
             asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_hi), "r"(f[3]) : "memory");
           }
         }
-        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_b(s));
+        if (kPairStages && pending < 0) {
+          pending = s;
+        } else {
+          fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core
+          __syncwarp();
+          if (lane == 0) {
+            if (pending >= 0) mbar_arrive(full_b(pending));
+            mbar_arrive(full_b(s));
+          }
+          pending = -1;
+        }
       }
+    }
+    if (pending >= 0) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_b(pending));
     }
   } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
     // ================= epilogue: TMEM -> registers -> C ==================================
@@ -518,8 +566,32 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Tensor map over the packed weights seen as [K/16 rows][N * bits * 2 bytes] of 8-byte
+// elements; box = 4 rows x (BN/64 tiles).
+static int make_b_map(CUtensorMap* map, const TcParams& p, int bits, int bn) {
+  const cuuint64_t row_elems = (cuuint64_t)p.n * bits * 2 / 8;  // 8-byte elements per k-tile row
+  const cuuint64_t gdim[2] = {row_elems, (cuuint64_t)(p.k / 16)};
+  const cuuint64_t gstride[1] = {row_elems * 8};
+  const int tile_elems = 16 * 64 * bits / 8 / 8;  // 8-byte elements per 16 x 64 tile
+  const int copy_tiles = (bn / 64) * tile_elems <= 256 ? (bn / 64) : 256 / tile_elems;
+  const cuuint32_t box[2] = {(cuuint32_t)(copy_tiles * tile_elems), 4};
+  const cuuint32_t estride[2] = {1, 1};
+  CUresult r = get_encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint32_t*>(p.b),
+                               gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B200Q_REQUIRE(r == CUDA_SUCCESS, B200Q_ECUDA, "cuTensorMapEncodeTiled (weights) failed with %d",
+                (int)r);
+  return B200Q_OK;
+}
+
 template <typename T, int BITS, bool HAS_ZP, int BM, int BN>
 static int launch_one(const CUtensorMap& map, const TcParams& p, cudaStream_t stream) {
+  CUtensorMap b_map;
+  {
+    const int rc = make_b_map(&b_map, p, BITS, BN);
+    if (rc != B200Q_OK) return rc;
+  }
   using Cfg = TcCfg<BM, BN, BITS>;
   auto kernel = gemm_tc_kernel<T, BITS, HAS_ZP, BM, BN>;
   static bool attr_done[64] = {};
@@ -533,7 +605,7 @@ static int launch_one(const CUtensorMap& map, const TcParams& p, cudaStream_t st
   const int tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
   const int sms = device_sm_count();
   const int grid = tiles < sms ? tiles : sms;
-  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map, p);
+  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map, b_map, p);
   note_launch();
   B200Q_CUDA_OK(cudaGetLastError());
   return B200Q_OK;
@@ -585,7 +657,10 @@ bool tc_gemm_supported(int64_t size_m, int64_t size_n, int64_t size_k, int gm) {
     min_m = e ? atoi(e) : 65;
     if (min_m < 1) min_m = 65;
   }
-  return size_m >= min_m && size_k % tc::kBK == 0 && size_n % 64 == 0 && gm != kLookup &&
+  // 33..64 rows: only where there are enough 128-column tiles to fill the GPU (measured: the
+  // 64-row decode kernel wins on narrower layers)
+  const bool rows_ok = size_m >= min_m || (size_m > 32 && size_n >= 16384);
+  return rows_ok && size_k % tc::kBK == 0 && size_n % 64 == 0 && gm != kLookup &&
          tc::get_encode_fn() != nullptr;  // group_blocks >= 2 is checked by the caller
 }
 
