@@ -49,9 +49,10 @@ int b200q_version(void);
  * GEMM workspace from this (marlin_utils.py:237-245). */
 int b200q_sm_count(void);
 
-/* Error word of the tensor-core GEMM on the current device: 0, or a code naming
- * the first hand-off wait that ran into its poll limit (the kernel then drains
- * and returns instead of hanging).  Synchronises the device.  reset != 0 clears
+/* Error word of the kernels that wait on hand-offs (tensor-core GEMM, all-reduce)
+ * on the current device: 0, or a code naming the first wait that ran into its
+ * poll limit (the kernel then drains and returns instead of hanging; codes with
+ * bit 16 set come from the all-reduce, low byte = peer rank).  Synchronises the device.  reset != 0 clears
  * it.  No counterpart in the reference, whose device-side waits are unbounded
  * (csrc/quantization/gptq_marlin/marlin_template.h:225-235). */
 int b200q_device_error(int reset);
@@ -131,6 +132,30 @@ int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q_weight,
                       int64_t workspace_len, int64_t b_q_type_id, int a_dtype,
                       int64_t size_m, int64_t size_n, int64_t size_k,
                       int64_t num_groups, unsigned flags, b200q_stream_t stream);
+
+/*
+ * One-shot SUM all-reduce of a 16-bit tensor across the ranks of a tensor-parallel
+ * group, over NVLink peer memory (plain loads / stores; fp32 accumulation in rank
+ * order, so every rank gets bitwise the same result).
+ * Replaces: the custom all-reduce behind RowParallelLinear's output,
+ *           csrc/custom_all_reduce.cu:62-105 / csrc/custom_all_reduce.cuh:298-314
+ *           (vllm/distributed/device_communicators/custom_all_reduce.py:267-283).
+ *   peer_bufs   device array [world] of every rank's data buffer (peer-mapped); the
+ *               message of this rank sits at peer_bufs[rank] + offset_bytes and must
+ *               be complete when the kernel starts (stream order)
+ *   peer_flags  device array [world] of every rank's flag array, each of
+ *               b200q_all_reduce_flag_bytes() bytes, zero before the first call
+ *   epochs      local device memory, b200q_all_reduce_epoch_bytes() bytes, zero
+ *               before the first call; advanced by the kernel (graph-replay safe)
+ *   out         local output [n_elems]; n_elems % 8 == 0
+ * All ranks must make the same sequence of calls with the same sizes.  Waits are
+ * bounded (see b200q_device_error).
+ */
+size_t b200q_all_reduce_flag_bytes(void);
+size_t b200q_all_reduce_epoch_bytes(void);
+int b200q_all_reduce(const void* const* peer_bufs, uint32_t* const* peer_flags, uint32_t* epochs,
+                     int rank, int world, int64_t offset_bytes, void* out, int64_t n_elems,
+                     int dtype, b200q_stream_t stream);
 
 /*
  * b200q_marlin_gemm for callers that cannot allocate device memory (a plugin

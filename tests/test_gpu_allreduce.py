@@ -1,0 +1,106 @@
+"""Peer-memory all-reduce (b200q_all_reduce) against NCCL on 2+ GPUs: exact
+equality on integer-valued inputs (as the reference's
+tests/distributed/test_custom_all_reduce.py:60-82 does), several sizes, repeated
+calls (the epoch counters), CUDA-graph replay, and a row-parallel quantized layer
+whose output goes through it.  Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from vllm_b200 import _lib
+    from vllm_b200 import distributed as D
+    D.initialize_model_parallel(world)
+    assert D.enable_custom_all_reduce(dev)
+    lib = _lib.load()
+    ok = True
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    for dtype in (torch.bfloat16, torch.float16):
+        for shape in ((1, 4096), (16, 4096), (64, 8192), (5, 8)):
+            for rep in range(3):
+                x = torch.randint(-8, 9, shape, device=dev, generator=gen).to(dtype)
+                want = x.clone()
+                dist.all_reduce(want)
+                got = D.tensor_model_parallel_all_reduce(x)
+                ok &= bool(torch.equal(got, want)) and got.data_ptr() != x.data_ptr()
+    # too large for the one-shot path: falls back to NCCL
+    big = torch.ones((1024, 8192), device=dev, dtype=torch.bfloat16)
+    ok &= bool((D.tensor_model_parallel_all_reduce(big) == world).all())
+    # CUDA graph replay: the kernel advances its own epochs
+    x = torch.randint(-8, 9, (16, 4096), device=dev, generator=gen).to(torch.bfloat16)
+    want = x.clone()
+    dist.all_reduce(want)
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        y = D.tensor_model_parallel_all_reduce(x)
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y = D.tensor_model_parallel_all_reduce(x)
+        y2 = D.tensor_model_parallel_all_reduce(y)
+    for _ in range(5):
+        g.replay()
+    torch.cuda.synchronize()
+    ok &= bool(torch.equal(y, want)) and bool(torch.equal(y2, want * world))
+    # a row-parallel quantized layer end to end
+    import numpy as np
+    from oracle import marlin_oracle as mo
+    from tests import gpu_utils as G
+    from tests import helpers as H
+    from vllm_b200.linear import RowParallelLinear
+    from vllm_b200.quantization import GPTQMarlinConfig
+    K, N, M, gsz = 2048, 1024, 16, 128
+    L = H.make_layer(K, N, "uint4b8", gsz, False, "bfloat16")
+    a_np = H.make_activations(M, K, "bfloat16")
+    layer = RowParallelLinear(K, N, quant_config=GPTQMarlinConfig(4, gsz, False),
+                              params_dtype=torch.bfloat16, device=dev)
+    layer.weight_loader(layer.qweight, torch.from_numpy(L.gptq_qweight).to(dev))
+    layer.weight_loader(layer.scales, torch.from_numpy(L.scales).to(torch.bfloat16).to(dev))
+    layer.weight_loader(layer.g_idx, torch.from_numpy((np.arange(K) // gsz).astype(np.int32)).to(dev))
+    layer.process_weights_after_loading()
+    a = G.t16(a_np, "bfloat16", device=dev)
+    out = layer(a[:, rank * K // world:(rank + 1) * K // world].contiguous())
+    torch.cuda.synchronize()
+    mf, mr = H.gemm_errors(G.n16(out), mo.gemm_ref(a_np, L.w))
+    ok &= mf <= H.MAX_ABS_FRAC and mr <= 2 * H.MEAN_REL
+    ok &= lib.b200q_device_error(1) == 0
+    q.put((rank, ok))
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)
+
+
+def test_custom_all_reduce_matches_nccl():
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=280) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok in results), results

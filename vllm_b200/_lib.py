@@ -25,6 +25,9 @@ EXPORTS = (
     "b200q_marlin_gemm",
     "b200q_marlin_gemm_noalloc_max_scratch",
     "b200q_marlin_gemm_noalloc",
+    "b200q_all_reduce_flag_bytes",
+    "b200q_all_reduce_epoch_bytes",
+    "b200q_all_reduce",
 )
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4
@@ -77,6 +80,10 @@ def load() -> ctypes.CDLL:
     lib.b200q_marlin_gemm_noalloc.restype = i32
     lib.b200q_marlin_gemm_noalloc.argtypes = [
         vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i64, i64, i64, i64, u32, vp]
+    lib.b200q_all_reduce_flag_bytes.restype = c.c_size_t
+    lib.b200q_all_reduce_epoch_bytes.restype = c.c_size_t
+    lib.b200q_all_reduce.restype = i32
+    lib.b200q_all_reduce.argtypes = [vp, vp, vp, i32, i32, i64, vp, i64, i32, vp]
     _lib = lib
     return lib
 

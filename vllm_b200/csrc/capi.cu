@@ -67,6 +67,7 @@ int launch_tc_gemm(const void* a, int64_t lda, const uint32_t* b, const void* sc
                    int64_t size_m, int64_t size_n, int64_t size_k, int group_blocks,
                    int channelwise, cudaStream_t stream);
 int tc_error_flag(bool reset);
+int ar_error_flag(bool reset);
 
 int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* out, int64_t size_m,
                         int64_t size_k, cudaStream_t stream);
@@ -117,7 +118,11 @@ extern "C" const char* b200q_last_error(void) { return g_error; }
 extern "C" int b200q_version(void) { return 100; }
 extern "C" unsigned long long b200q_kernel_launches(void) { return g_launches.load(); }
 extern "C" int b200q_sm_count(void) { return device_sm_count(); }
-extern "C" int b200q_device_error(int reset) { return tc_error_flag(reset != 0); }
+extern "C" int b200q_device_error(int reset) {
+  const int tc = tc_error_flag(reset != 0);
+  const int ar = ar_error_flag(reset != 0);
+  return tc != 0 ? tc : (ar != 0 ? (0x10000 | ar) : 0);
+}
 
 extern "C" size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
                                                   int has_act_order) {

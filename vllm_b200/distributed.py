@@ -15,6 +15,7 @@ import torch.distributed as dist
 _TP_GROUP = None
 _TP_RANK = 0
 _TP_SIZE = 1
+_CUSTOM_AR = None
 
 
 def initialize_model_parallel(tensor_model_parallel_size: int | None = None, group=None) -> None:
@@ -33,9 +34,20 @@ def initialize_model_parallel(tensor_model_parallel_size: int | None = None, gro
                          f"process group has {_TP_SIZE} ranks")
 
 
+def enable_custom_all_reduce(device: torch.device, max_size: int = 1 << 20) -> bool:
+    """Set up the peer-memory all-reduce for small messages (decode).  Collective: call on
+    every rank after initialize_model_parallel.  Returns whether it is active."""
+    global _CUSTOM_AR
+    if _TP_SIZE < 2:
+        return False
+    from .custom_all_reduce import CustomAllreduce
+    _CUSTOM_AR = CustomAllreduce(_TP_GROUP, device, max_size)
+    return not _CUSTOM_AR.disabled
+
+
 def destroy_model_parallel() -> None:
-    global _TP_GROUP, _TP_RANK, _TP_SIZE
-    _TP_GROUP, _TP_RANK, _TP_SIZE = None, 0, 1
+    global _TP_GROUP, _TP_RANK, _TP_SIZE, _CUSTOM_AR
+    _TP_GROUP, _TP_RANK, _TP_SIZE, _CUSTOM_AR = None, 0, 1, None
 
 
 def get_tensor_model_parallel_world_size() -> int:
@@ -51,6 +63,10 @@ def tensor_model_parallel_all_reduce(input_: torch.Tensor) -> torch.Tensor:
     is out-of-place, parallel_state.py:117-126)."""
     if _TP_SIZE == 1:
         return input_
+    if _CUSTOM_AR is not None:
+        out = _CUSTOM_AR.custom_all_reduce(input_)
+        if out is not None:
+            return out
     out = input_.clone()
     dist.all_reduce(out, op=dist.ReduceOp.SUM, group=_TP_GROUP)
     return out
