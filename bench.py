@@ -153,7 +153,7 @@ def run_reference(args, world, rank):
         t_s += s
     value = t_bytes / t_s / 1e9
     sample = "QKV 4096->6144 at M=16 per step (unpack + act-order dequant + fp32 matmul, numpy)"
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_s / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -161,14 +161,15 @@ def run_reference(args, world, rank):
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }), flush=True)
+    })
 
 
 def workload_config(world):
     return {"workload": "llama3_8b_gptq_uint4b8_g128_actorder_layer_sweep",
             "layers_k_n": [[k, n] for _, k, n, _ in LAYERS], "m_values": MS,
             "group_size": GROUP, "act_order": True,
-            "parallelism": "tp%d_weak (per-GPU shard shapes fixed; O/down all-reduce)" % world
+            "parallelism": "tp%d_weak (per-GPU shard shapes fixed; O/down all-reduce: peer-memory "
+                           "kernel up to 512 KiB, NCCL above)" % world
             if world > 1 else "single_gpu",
             "l2_policy": "weight pool of >= 400 MB per layer rotated per call (inputs larger than L2)"}
 
@@ -210,9 +211,15 @@ def run_ours(args, world, rank, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
+    custom_ar = None
     if world > 1:
         import torch.distributed as dist
+
+        from vllm_b200 import distributed as D
         dist.init_process_group("nccl", device_id=dev)
+        D.initialize_model_parallel(world)
+        if os.environ.get("BENCH_NCCL_ONLY", "0") != "1" and D.enable_custom_all_reduce(dev):
+            custom_ar = D._CUSTOM_AR
     lib = _lib.load()
     dt = torch.bfloat16
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -230,13 +237,16 @@ def run_ours(args, world, rank, local_rank):
     def raw_call(p, m, copy):
         """One GEMM through the C ABI on the current stream, inputs resident in HBM."""
         a, c = a_dev[(p.k, m)], c_dev[(p.n, m)]
+        fused = (custom_ar is not None and p.row_parallel and m * p.n * 2 <= custom_ar.max_size)
         rc = lib.b200q_marlin_gemm(
             vp(a.data_ptr()), p.k, vp(p.q[copy].data_ptr()), vp(p.s[copy].data_ptr()), None,
             vp(p.g_idx.data_ptr()), vp(p.perm.data_ptr()), None, vp(c.data_ptr()),
             vp(scratch.data_ptr()), max_scratch, vp(ws.data_ptr()), ws.numel(), qtype.id, _lib.BF16,
             m, p.n, p.k, p.k // GROUP, flags, vp(torch.cuda.current_stream().cuda_stream))
         _lib.check(rc, "b200q_marlin_gemm")
-        if dist is not None and p.row_parallel:
+        if fused:
+            custom_ar.custom_all_reduce(c)            # one kernel over NVLink peer memory
+        elif dist is not None and p.row_parallel:
             dist.all_reduce(c)
 
     shapes = [(p, m) for p in pools for m in MS]
@@ -314,7 +324,7 @@ def run_ours(args, world, rank, local_rank):
                                    ws, qtype, m, p.n, p.k, is_k_full=True, use_atomic_add=False,
                                    use_fp32_reduce=True, is_zp_float=False)
         if dist is not None and p.row_parallel:
-            dist.all_reduce(out)
+            out = D.tensor_model_parallel_all_reduce(out)
         c_host[(p.n, m)].copy_(out, non_blocking=True)
 
     for p, m in shapes:
@@ -400,10 +410,24 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks):
             "value": b / s / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
             "sample": "the four layers at M=16, one pass (unpack + act-order dequant + fp32 matmul, "
                       "numpy restatement of the reference's CPU path), %.1f s" % s}
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+_RESULT_FD = 1
+
+
+def emit(line: dict) -> None:
+    """Write the result line to the process's original stdout."""
+    os.write(_RESULT_FD, (json.dumps(line) + "\n").encode())
 
 
 def main():
+    # libraries (NCCL's version banner, for one) print to file descriptor 1: keep it for the
+    # single result line and send everything else to stderr
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

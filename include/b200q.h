@@ -140,22 +140,23 @@ int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q_weight,
  * Replaces: the custom all-reduce behind RowParallelLinear's output,
  *           csrc/custom_all_reduce.cu:62-105 / csrc/custom_all_reduce.cuh:298-314
  *           (vllm/distributed/device_communicators/custom_all_reduce.py:267-283).
- *   peer_bufs   device array [world] of every rank's data buffer (peer-mapped); the
- *               message of this rank sits at peer_bufs[rank] + offset_bytes and must
- *               be complete when the kernel starts (stream order)
+ *   peer_bufs   device array [world] of every rank's receive buffer (peer-mapped), each
+ *               of b200q_all_reduce_buffer_bytes(world, max_message_bytes) bytes
  *   peer_flags  device array [world] of every rank's flag array, each of
  *               b200q_all_reduce_flag_bytes() bytes, zero before the first call
  *   epochs      local device memory, b200q_all_reduce_epoch_bytes() bytes, zero
  *               before the first call; advanced by the kernel (graph-replay safe)
- *   out         local output [n_elems]; n_elems % 8 == 0
+ *   in          this rank's partial [n_elems], local memory, complete in stream order
+ *   out         local output [n_elems]; n_elems % 8 == 0, n_elems * 2 <= max_message_bytes
  * All ranks must make the same sequence of calls with the same sizes.  Waits are
  * bounded (see b200q_device_error).
  */
 size_t b200q_all_reduce_flag_bytes(void);
 size_t b200q_all_reduce_epoch_bytes(void);
-int b200q_all_reduce(const void* const* peer_bufs, uint32_t* const* peer_flags, uint32_t* epochs,
-                     int rank, int world, int64_t offset_bytes, void* out, int64_t n_elems,
-                     int dtype, b200q_stream_t stream);
+size_t b200q_all_reduce_buffer_bytes(int world, int64_t max_message_bytes);
+int b200q_all_reduce(void* const* peer_bufs, uint32_t* const* peer_flags, uint32_t* epochs,
+                     int rank, int world, int64_t max_message_bytes, const void* in, void* out,
+                     int64_t n_elems, int dtype, b200q_stream_t stream);
 
 /*
  * b200q_marlin_gemm for callers that cannot allocate device memory (a plugin

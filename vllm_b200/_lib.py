@@ -27,6 +27,7 @@ EXPORTS = (
     "b200q_marlin_gemm_noalloc",
     "b200q_all_reduce_flag_bytes",
     "b200q_all_reduce_epoch_bytes",
+    "b200q_all_reduce_buffer_bytes",
     "b200q_all_reduce",
 )
 
@@ -83,7 +84,9 @@ def load() -> ctypes.CDLL:
     lib.b200q_all_reduce_flag_bytes.restype = c.c_size_t
     lib.b200q_all_reduce_epoch_bytes.restype = c.c_size_t
     lib.b200q_all_reduce.restype = i32
-    lib.b200q_all_reduce.argtypes = [vp, vp, vp, i32, i32, i64, vp, i64, i32, vp]
+    lib.b200q_all_reduce_buffer_bytes.restype = c.c_size_t
+    lib.b200q_all_reduce_buffer_bytes.argtypes = [i32, i64]
+    lib.b200q_all_reduce.argtypes = [vp, vp, vp, i32, i32, i64, vp, vp, i64, i32, vp]
     _lib = lib
     return lib
 

@@ -1,23 +1,27 @@
 // One-shot all-reduce of the row-parallel GEMM output over NVLink peer memory.
 //
-// Every rank keeps its partial result in a buffer that all ranks of the
-// tensor-parallel group can address (peer pointers; plain loads and stores over
-// NVLink / NVSwitch, no multicast).  One kernel per rank:
-//   1. start barrier  - block b of every rank tells block b of every peer that
-//                       its partial is complete (flag = epoch + 1) and waits for
-//                       the peers' flags;
-//   2. reduce         - 16-byte vectors are read from every rank's buffer and
-//                       summed in fp32 in rank order, so all ranks produce
-//                       bitwise identical results, then rounded once and stored;
-//   3. end barrier    - flag = epoch + 2: nobody returns (and lets its next GEMM
-//                       overwrite the buffer) while a peer may still be reading.
-// The epoch lives in device memory, one counter per block, and advances by 2 per
-// call, so a captured CUDA graph can replay the kernel.  Flags only ever grow:
-// no reset traffic.  Every wait is bounded; on time-out the kernel records an
-// error word and returns without reducing.
+// Every rank owns a receive buffer that all ranks of the tensor-parallel group
+// can address (peer pointers; plain stores over NVLink / NVSwitch, no multicast),
+// laid out as [2 parities][world slots][slot_bytes].  One kernel per rank:
+//   1. push     - block b stores its share of this rank's partial (read from local
+//                 memory) into slot `rank` of every peer's buffer, parity = call
+//                 number mod 2;
+//   2. signal   - after the block's stores, one thread per peer publishes
+//                 flag[b][rank] = epoch + 1 in that peer's flag array
+//                 (st.release.sys) and waits for the peer's flag in its own array;
+//   3. reduce   - the block sums the slots of its own buffer (local reads) and its
+//                 own partial in rank order with fp32 accumulation, so all ranks
+//                 produce bitwise identical results, rounds once and stores.
+// One flag round per call: a rank can only be two calls ahead of a peer after the
+// peer has signalled the call in between, i.e. finished reading the parity that is
+// about to be overwritten.  The call number lives in device memory, one counter
+// per block, advanced by the kernel, so a captured CUDA graph can replay it.
+// Flags only ever grow: no reset traffic.  Every wait is bounded; on time-out the
+// kernel records an error word and returns without reducing.
 //
 // The counterpart in the reference is the custom all-reduce of
-// csrc/custom_all_reduce.cuh:298-314 (one-stage variant, unbounded waits there).
+// csrc/custom_all_reduce.cuh:298-314 (one-stage variant, pull-based, two barriers,
+// unbounded waits).
 #include "common.cuh"
 
 namespace b200q {
@@ -31,11 +35,12 @@ constexpr uint32_t kSpinLimit = 1u << 22;  // polls of a local flag: seconds at 
 __device__ int g_ar_error;  // 0 = ok, else 0x100 | peer rank of the first wait that timed out
 
 struct ArParams {
-  const void* const* bufs;      // device array [world]: every rank's data buffer
-  uint32_t* const* flags;       // device array [world]: every rank's flag array [kMaxBlocks * 2 * world]
-  uint32_t* epochs;             // local: one counter per block
+  void* const* bufs;            // device array [world]: every rank's receive buffer
+  uint32_t* const* flags;       // device array [world]: every rank's flag array [kMaxBlocks * world]
+  uint32_t* epochs;             // local: one call counter per block
+  const void* in;               // local partial
   void* out;                    // local output
-  long long offset_bytes;       // offset of the message inside the data buffers
+  long long slot_bytes;         // size of one (parity, rank) slot of a receive buffer
   long long n_vec;              // 16-byte vectors in the message
   int rank, world;
 };
@@ -49,32 +54,6 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// Threads 0..world-1 of the block each handle one peer: signal it, then wait for it.
-// `phase` 0 = start flags, 1 = end flags.  Returns false for the whole block on time-out.
-__device__ __forceinline__ bool block_barrier(const ArParams& p, uint32_t target, int phase,
-                                              int* s_fail) {
-  const int t = threadIdx.x;
-  if (t < p.world) {
-    // my slot in peer t's array: [block][phase][source rank]
-    uint32_t* theirs = p.flags[t] + ((blockIdx.x * 2 + phase) * p.world + p.rank);
-    st_release_sys(theirs, target);
-    const uint32_t* mine = p.flags[p.rank] + ((blockIdx.x * 2 + phase) * p.world + t);
-    bool ok = false;
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-      if ((int32_t)(ld_acquire_sys(mine) - target) >= 0) {
-        ok = true;
-        break;
-      }
-    }
-    if (!ok) {
-      *s_fail = 1;
-      atomicCAS(&g_ar_error, 0, 0x100 | t);
-    }
-  }
-  __syncthreads();
-  return *s_fail == 0;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kThreads) allreduce_oneshot_kernel(const ArParams p) {
   __shared__ uint32_t s_epoch;
@@ -85,21 +64,56 @@ __global__ void __launch_bounds__(kThreads) allreduce_oneshot_kernel(const ArPar
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   if (threadIdx.x == 0) {
     s_epoch = p.epochs[blockIdx.x];
-    p.epochs[blockIdx.x] = s_epoch + 2;
+    p.epochs[blockIdx.x] = s_epoch + 1;
     s_fail = 0;
   }
   __syncthreads();
   const uint32_t epoch = s_epoch;
-  if (!block_barrier(p, epoch + 1, 0, &s_fail)) return;
-
+  const long long parity_off = (long long)(epoch & 1) * p.world * p.slot_bytes;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < p.n_vec; v += stride) {
+  const long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint4* in = static_cast<const uint4*>(p.in);
+
+  // 1. push this block's vectors into slot `rank` of every peer
+  for (long long v = v0; v < p.n_vec; v += stride) {
+    const uint4 x = in[v];
+    for (int r = 0; r < p.world; ++r) {
+      if (r == p.rank) continue;
+      char* dst = static_cast<char*>(p.bufs[r]) + parity_off + p.rank * p.slot_bytes;
+      reinterpret_cast<uint4*>(dst)[v] = x;
+    }
+  }
+  __syncthreads();
+  // 2. signal every peer, wait for every peer (threads 0 .. world-1, one peer each)
+  if (threadIdx.x < p.world && threadIdx.x != p.rank) {
+    const int t = threadIdx.x;
+    st_release_sys(p.flags[t] + (blockIdx.x * p.world + p.rank), epoch + 1);
+    const uint32_t* mine = p.flags[p.rank] + (blockIdx.x * p.world + t);
+    bool ok = false;
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+      if ((int32_t)(ld_acquire_sys(mine) - (epoch + 1)) >= 0) {
+        ok = true;
+        break;
+      }
+    }
+    if (!ok) {
+      s_fail = 1;
+      atomicCAS(&g_ar_error, 0, 0x100 | t);
+    }
+  }
+  __syncthreads();
+  if (s_fail) return;
+
+  // 3. reduce in rank order from local memory
+  const char* mybuf = static_cast<const char*>(p.bufs[p.rank]) + parity_off;
+  for (long long v = v0; v < p.n_vec; v += stride) {
     float acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
     for (int r = 0; r < p.world; ++r) {
-      const uint4 x = *reinterpret_cast<const uint4*>(static_cast<const char*>(p.bufs[r]) +
-                                                      p.offset_bytes + v * 16);
+      const uint4 x = (r == p.rank)
+                          ? in[v]
+                          : __ldcv(reinterpret_cast<const uint4*>(mybuf + r * p.slot_bytes) + v);
       const uint32_t w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -114,8 +128,6 @@ __global__ void __launch_bounds__(kThreads) allreduce_oneshot_kernel(const ArPar
     o.w = (uint32_t)Pair<T>::from_float(acc[6]) | ((uint32_t)Pair<T>::from_float(acc[7]) << 16);
     reinterpret_cast<uint4*>(p.out)[v] = o;
   }
-  __syncthreads();
-  block_barrier(p, epoch + 2, 1, &s_fail);
 }
 
 }  // namespace ar
@@ -135,31 +147,39 @@ int ar_error_flag(bool reset) {
 using namespace b200q;
 
 extern "C" size_t b200q_all_reduce_flag_bytes(void) {
-  return (size_t)ar::kMaxBlocks * 2 * ar::kMaxWorld * sizeof(uint32_t);
+  return (size_t)ar::kMaxBlocks * ar::kMaxWorld * sizeof(uint32_t);
 }
 extern "C" size_t b200q_all_reduce_epoch_bytes(void) { return ar::kMaxBlocks * sizeof(uint32_t); }
+extern "C" size_t b200q_all_reduce_buffer_bytes(int world, int64_t max_message_bytes) {
+  return (size_t)2 * (size_t)world * (size_t)max_message_bytes;
+}
 
-extern "C" int b200q_all_reduce(const void* const* peer_bufs, uint32_t* const* peer_flags,
-                                uint32_t* epochs, int rank, int world, int64_t offset_bytes,
-                                void* out, int64_t n_elems, int dtype, b200q_stream_t stream_) {
+extern "C" int b200q_all_reduce(void* const* peer_bufs, uint32_t* const* peer_flags,
+                                uint32_t* epochs, int rank, int world, int64_t max_message_bytes,
+                                const void* in, void* out, int64_t n_elems, int dtype,
+                                b200q_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   B200Q_REQUIRE(world >= 2 && world <= ar::kMaxWorld, B200Q_EINVAL,
                 "all-reduce world size %d is not in [2, %d]", world, ar::kMaxWorld);
   B200Q_REQUIRE(rank >= 0 && rank < world, B200Q_EINVAL, "rank %d out of range", rank);
   B200Q_REQUIRE(dtype == B200Q_F16 || dtype == B200Q_BF16, B200Q_EINVAL, "dtype must be fp16/bf16");
-  B200Q_REQUIRE(peer_bufs && peer_flags && epochs && out, B200Q_EINVAL, "null pointer");
-  B200Q_REQUIRE(n_elems >= 0 && n_elems % 8 == 0 && offset_bytes % 16 == 0, B200Q_EINVAL,
+  B200Q_REQUIRE(peer_bufs && peer_flags && epochs && in && out, B200Q_EINVAL, "null pointer");
+  B200Q_REQUIRE(n_elems >= 0 && n_elems % 8 == 0, B200Q_EINVAL,
                 "message must be a whole number of 16-byte vectors (n_elems = %lld)",
                 (long long)n_elems);
-  B200Q_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0, B200Q_EINVAL,
-                "out must be aligned to 16 bytes");
+  B200Q_REQUIRE(max_message_bytes % 16 == 0 && n_elems * 2 <= max_message_bytes, B200Q_EINVAL,
+                "message of %lld bytes exceeds the slot size %lld", (long long)n_elems * 2,
+                (long long)max_message_bytes);
+  B200Q_REQUIRE(((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in)) & 15) == 0,
+                B200Q_EINVAL, "in / out must be aligned to 16 bytes");
   if (n_elems == 0) return B200Q_OK;
   ar::ArParams p;
   p.bufs = peer_bufs;
   p.flags = peer_flags;
   p.epochs = epochs;
+  p.in = in;
   p.out = out;
-  p.offset_bytes = offset_bytes;
+  p.slot_bytes = max_message_bytes;
   p.n_vec = n_elems / 8;
   p.rank = rank;
   p.world = world;

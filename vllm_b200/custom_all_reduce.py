@@ -21,7 +21,7 @@ from . import _lib
 class CustomAllreduce:
     # messages above this go to NCCL (the reference caps its one-stage kernel at 256-512 KiB,
     # csrc/custom_all_reduce.cuh:592-593, and the whole path at 1-2 MiB on compute capability 10.0)
-    def __init__(self, group, device: torch.device, max_size: int = 1 << 20) -> None:
+    def __init__(self, group, device: torch.device, max_size: int = 1 << 19) -> None:
         import torch.distributed._symmetric_memory as symm_mem
         self.lib = _lib.load()
         self.group = group
@@ -33,7 +33,8 @@ class CustomAllreduce:
         if self.world_size < 2 or self.world_size > 8:
             return
         symm_mem.enable_symm_mem_for_group(group.group_name)
-        self.data = symm_mem.empty(max_size, dtype=torch.uint8, device=device)
+        self.data = symm_mem.empty(self.lib.b200q_all_reduce_buffer_bytes(self.world_size, max_size),
+                                   dtype=torch.uint8, device=device)
         self.data_hdl = symm_mem.rendezvous(self.data, group.group_name)
         nflag = self.lib.b200q_all_reduce_flag_bytes() // 4
         self.flags = symm_mem.empty(nflag, dtype=torch.int32, device=device)
@@ -49,29 +50,21 @@ class CustomAllreduce:
         if self.disabled or not inp.is_cuda or inp.dtype not in (torch.float16, torch.bfloat16):
             return False
         nbytes = inp.numel() * inp.element_size()
-        return nbytes % 16 == 0 and 0 < nbytes <= self.max_size and inp.is_contiguous()
-
-    def buffer_like(self, shape, dtype) -> torch.Tensor:
-        """A view of this rank's peer-visible buffer: a GEMM that writes its output here saves
-        the staging copy of ``custom_all_reduce``."""
-        n = 1
-        for d in shape:
-            n *= d
-        return self.data[: n * torch.empty((), dtype=dtype).element_size()].view(dtype).view(*shape)
+        return (nbytes % 16 == 0 and 0 < nbytes <= self.max_size and inp.is_contiguous()
+                and inp.data_ptr() % 16 == 0)
 
     def custom_all_reduce(self, inp: torch.Tensor) -> torch.Tensor | None:
-        """Out-of-place SUM all-reduce, or None when the input does not qualify."""
+        """Out-of-place SUM all-reduce, or None when the input does not qualify.  The input is
+        read where it is (no staging copy): the kernel pushes it into the peers' buffers."""
         if not self.should_custom_ar(inp):
             return None
-        nbytes = inp.numel() * inp.element_size()
-        if inp.data_ptr() != self.data.data_ptr():
-            self.data[:nbytes].view(inp.dtype).view(inp.shape).copy_(inp)   # stage (as the reference does)
         out = torch.empty_like(inp)
         vp = ctypes.c_void_p
         rc = self.lib.b200q_all_reduce(
             vp(self.data_hdl.buffer_ptrs_dev), vp(self.flags_hdl.buffer_ptrs_dev),
-            vp(self.epochs.data_ptr()), self.rank, self.world_size, 0, vp(out.data_ptr()),
-            inp.numel(), _lib.BF16 if inp.dtype == torch.bfloat16 else _lib.F16,
+            vp(self.epochs.data_ptr()), self.rank, self.world_size, self.max_size,
+            vp(inp.data_ptr()), vp(out.data_ptr()), inp.numel(),
+            _lib.BF16 if inp.dtype == torch.bfloat16 else _lib.F16,
             vp(torch.cuda.current_stream(self.device).cuda_stream))
         _lib.check(rc, "b200q_all_reduce")
         return out

@@ -34,7 +34,7 @@ def initialize_model_parallel(tensor_model_parallel_size: int | None = None, gro
                          f"process group has {_TP_SIZE} ranks")
 
 
-def enable_custom_all_reduce(device: torch.device, max_size: int = 1 << 20) -> bool:
+def enable_custom_all_reduce(device: torch.device, max_size: int = 1 << 19) -> bool:
     """Set up the peer-memory all-reduce for small messages (decode).  Collective: call on
     every rank after initialize_model_parallel.  Returns whether it is active."""
     global _CUSTOM_AR
