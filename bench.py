@@ -168,8 +168,8 @@ def workload_config(world):
     return {"workload": "llama3_8b_gptq_uint4b8_g128_actorder_layer_sweep",
             "layers_k_n": [[k, n] for _, k, n, _ in LAYERS], "m_values": MS,
             "group_size": GROUP, "act_order": True,
-            "parallelism": "tp%d_weak (per-GPU shard shapes fixed; O/down all-reduce: peer-memory "
-                           "kernel up to 512 KiB, NCCL above)" % world
+            "parallelism": "tp%d_weak (per-GPU shard shapes fixed; O/down all-reduce over NVLink peer "
+                           "memory up to 512 KiB - inside the GEMM kernel at M <= 32 - NCCL above)" % world
             if world > 1 else "single_gpu",
             "l2_policy": "weight pool of >= 400 MB per layer rotated per call (inputs larger than L2)"}
 
@@ -211,7 +211,7 @@ def run_ours(args, world, rank, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
-    custom_ar = None
+    custom_ar = ar_link = None
     if world > 1:
         import torch.distributed as dist
 
@@ -220,6 +220,7 @@ def run_ours(args, world, rank, local_rank):
         D.initialize_model_parallel(world)
         if os.environ.get("BENCH_NCCL_ONLY", "0") != "1" and D.enable_custom_all_reduce(dev):
             custom_ar = D._CUSTOM_AR
+            ar_link = D.fused_all_reduce_scope().link_args()
     lib = _lib.load()
     dt = torch.bfloat16
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -238,15 +239,19 @@ def run_ours(args, world, rank, local_rank):
         """One GEMM through the C ABI on the current stream, inputs resident in HBM."""
         a, c = a_dev[(p.k, m)], c_dev[(p.n, m)]
         fused = (custom_ar is not None and p.row_parallel and m * p.n * 2 <= custom_ar.max_size)
-        rc = lib.b200q_marlin_gemm(
-            vp(a.data_ptr()), p.k, vp(p.q[copy].data_ptr()), vp(p.s[copy].data_ptr()), None,
-            vp(p.g_idx.data_ptr()), vp(p.perm.data_ptr()), None, vp(c.data_ptr()),
-            vp(scratch.data_ptr()), max_scratch, vp(ws.data_ptr()), ws.numel(), qtype.id, _lib.BF16,
-            m, p.n, p.k, p.k // GROUP, flags, vp(torch.cuda.current_stream().cuda_stream))
-        _lib.check(rc, "b200q_marlin_gemm")
+        args = (vp(a.data_ptr()), p.k, vp(p.q[copy].data_ptr()), vp(p.s[copy].data_ptr()), None,
+                vp(p.g_idx.data_ptr()), vp(p.perm.data_ptr()), None, vp(c.data_ptr()),
+                vp(scratch.data_ptr()), max_scratch, vp(ws.data_ptr()), ws.numel(), qtype.id,
+                _lib.BF16, m, p.n, p.k, p.k // GROUP, flags)
+        cur = vp(torch.cuda.current_stream().cuda_stream)
         if fused:
-            custom_ar.custom_all_reduce(c)            # one kernel over NVLink peer memory
-        elif dist is not None and p.row_parallel:
+            # GEMM and all-reduce in one call: one kernel at M <= 32, GEMM + peer-memory
+            # all-reduce kernel above
+            rc = lib.b200q_marlin_gemm_all_reduce(*args, *ar_link, cur)
+        else:
+            rc = lib.b200q_marlin_gemm(*args, cur)
+        _lib.check(rc, "b200q_marlin_gemm")
+        if not fused and dist is not None and p.row_parallel:
             dist.all_reduce(c)
 
     shapes = [(p, m) for p in pools for m in MS]

@@ -141,22 +141,41 @@ int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q_weight,
  *           csrc/custom_all_reduce.cu:62-105 / csrc/custom_all_reduce.cuh:298-314
  *           (vllm/distributed/device_communicators/custom_all_reduce.py:267-283).
  *   peer_bufs   device array [world] of every rank's receive buffer (peer-mapped), each
- *               of b200q_all_reduce_buffer_bytes(world, max_message_bytes) bytes
- *   peer_flags  device array [world] of every rank's flag array, each of
- *               b200q_all_reduce_flag_bytes() bytes, zero before the first call
- *   epochs      local device memory, b200q_all_reduce_epoch_bytes() bytes, zero
- *               before the first call; advanced by the kernel (graph-replay safe)
+ *               of b200q_all_reduce_buffer_bytes(world, max_message_bytes) bytes, zero
+ *               before the first call
+ *   state       local device memory, b200q_all_reduce_state_bytes() bytes, zero
+ *               before the first call; the kernels keep the call number there, so
+ *               a captured CUDA graph can be replayed
  *   in          this rank's partial [n_elems], local memory, complete in stream order
- *   out         local output [n_elems]; n_elems % 8 == 0, n_elems * 2 <= max_message_bytes
- * All ranks must make the same sequence of calls with the same sizes.  Waits are
- * bounded (see b200q_device_error).
+ *   out         local output [n_elems] (may be `in`); n_elems % 8 == 0,
+ *               n_elems * 2 <= max_message_bytes
+ * All ranks must make the same sequence of calls (of this function and of
+ * b200q_marlin_gemm_all_reduce) with the same sizes on one link.  Waits are bounded
+ * (see b200q_device_error).
  */
-size_t b200q_all_reduce_flag_bytes(void);
-size_t b200q_all_reduce_epoch_bytes(void);
+size_t b200q_all_reduce_state_bytes(void);
 size_t b200q_all_reduce_buffer_bytes(int world, int64_t max_message_bytes);
-int b200q_all_reduce(void* const* peer_bufs, uint32_t* const* peer_flags, uint32_t* epochs,
-                     int rank, int world, int64_t max_message_bytes, const void* in, void* out,
-                     int64_t n_elems, int dtype, b200q_stream_t stream);
+int b200q_all_reduce(void* const* peer_bufs, uint32_t* state, int rank, int world,
+                     int64_t max_message_bytes, const void* in, void* out, int64_t n_elems,
+                     int dtype, b200q_stream_t stream);
+
+/*
+ * b200q_marlin_gemm followed by the SUM all-reduce of C over the same peer link, as
+ * RowParallelLinear does (vllm/model_executor/layers/linear.py:1386-1411: the
+ * quantized matmul of the K shard, then tensor_model_parallel_all_reduce).  Where one
+ * decode launch covers the problem (size_m <= 32) the GEMM kernel itself pushes its
+ * rounded output tile to the peers and reduces: one kernel, no second launch;
+ * otherwise the all-reduce kernel runs on C in place.  The result equals
+ * b200q_marlin_gemm + b200q_all_reduce bit for bit.
+ * size_m * size_n * 2 <= max_message_bytes; the other arguments as in the two calls.
+ */
+int b200q_marlin_gemm_all_reduce(
+    const void* a, int64_t lda, const uint32_t* b_q_weight, const void* b_scales,
+    const uint32_t* b_zeros, const int32_t* g_idx, const int32_t* perm, const void* b_bias,
+    void* c, void* scratch, size_t scratch_bytes, int32_t* workspace, int64_t workspace_len,
+    int64_t b_q_type_id, int a_dtype, int64_t size_m, int64_t size_n, int64_t size_k,
+    int64_t num_groups, unsigned flags, void* const* peer_bufs, uint32_t* state, int rank,
+    int world, int64_t max_message_bytes, b200q_stream_t stream);
 
 /*
  * b200q_marlin_gemm for callers that cannot allocate device memory (a plugin

@@ -77,10 +77,32 @@ def _worker(rank, world, port, q):
     layer.weight_loader(layer.g_idx, torch.from_numpy((np.arange(K) // gsz).astype(np.int32)).to(dev))
     layer.process_weights_after_loading()
     a = G.t16(a_np, "bfloat16", device=dev)
-    out = layer(a[:, rank * K // world:(rank + 1) * K // world].contiguous())
+    shard = a[:, rank * K // world:(rank + 1) * K // world].contiguous()
+    out = layer(shard)                      # GEMM with the all-reduce in its epilogue
     torch.cuda.synchronize()
     mf, mr = H.gemm_errors(G.n16(out), mo.gemm_ref(a_np, L.w))
     ok &= mf <= H.MAX_ABS_FRAC and mr <= 2 * H.MEAN_REL
+    # the fused kernel gives the bits of GEMM followed by the stand-alone all-reduce, for
+    # every decode size, for sizes that take the in-place kernel (M = 48), and under graph replay
+    for m in (1, 3, 8, 16, 32, 48):
+        part = layer.quant_method.apply(layer, shard[:m].contiguous(), None)
+        want = D.tensor_model_parallel_all_reduce(part)
+        got = layer(shard[:m].contiguous())
+        ok &= bool(torch.equal(got, want))
+    xs = shard[:16].contiguous()
+    want = D.tensor_model_parallel_all_reduce(layer.quant_method.apply(layer, xs, None))
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer(xs)
+    torch.cuda.current_stream().wait_stream(side)
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g2):
+        o1 = layer(xs)
+        o2 = layer(xs)
+    for _ in range(7):
+        g2.replay()
+    torch.cuda.synchronize()
+    ok &= bool(torch.equal(o1, want)) and bool(torch.equal(o2, want))
     ok &= lib.b200q_device_error(1) == 0
     q.put((rank, ok))
     dist.barrier()

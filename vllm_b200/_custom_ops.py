@@ -20,6 +20,7 @@ import os
 import torch
 
 from . import _lib
+from . import custom_all_reduce as _car
 from .scalar_type import ScalarType
 
 _L = _lib.load()  # raises if the CUDA library is absent
@@ -279,11 +280,17 @@ def _gptq_marlin_gemm_cuda(a, c_or_none, b_q_weight, b_bias_or_none, b_scales, g
         flags = ((_lib.FLAG_K_FULL if is_k_full else 0)
                  | (_lib.FLAG_ATOMIC_ADD if use_atomic_add else 0)
                  | (_lib.FLAG_FP32_REDUCE if use_fp32_reduce else 0))
-        rc = _L.b200q_marlin_gemm(
-            _ptr(a), a.stride(0), _ptr(b_q_weight), _ptr(b_scales), _ptr(zeros), _ptr(g_idx),
-            _ptr(perm), _ptr(bias), _ptr(c), _ptr(scratch), nbytes, _ptr(workspace),
-            workspace.numel(), b_q_type, _lib.BF16 if a.dtype == torch.bfloat16 else _lib.F16,
-            size_m, size_n, size_k, num_groups, flags, _stream(a.device))
+        args = (_ptr(a), a.stride(0), _ptr(b_q_weight), _ptr(b_scales), _ptr(zeros), _ptr(g_idx),
+                _ptr(perm), _ptr(bias), _ptr(c), _ptr(scratch), nbytes, _ptr(workspace),
+                workspace.numel(), b_q_type, _lib.BF16 if a.dtype == torch.bfloat16 else _lib.F16,
+                size_m, size_n, size_k, num_groups, flags)
+        scope = _car.active_scope()
+        if scope is not None and scope.accepts(c):
+            # row-parallel layer: the GEMM all-reduces its own output over the peer link
+            rc = _L.b200q_marlin_gemm_all_reduce(*args, *scope.link_args(), _stream(a.device))
+            scope.done = True
+        else:
+            rc = _L.b200q_marlin_gemm(*args, _stream(a.device))
     _lib.check(rc, "gptq_marlin_gemm")
     return c
 

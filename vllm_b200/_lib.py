@@ -25,10 +25,10 @@ EXPORTS = (
     "b200q_marlin_gemm",
     "b200q_marlin_gemm_noalloc_max_scratch",
     "b200q_marlin_gemm_noalloc",
-    "b200q_all_reduce_flag_bytes",
-    "b200q_all_reduce_epoch_bytes",
+    "b200q_all_reduce_state_bytes",
     "b200q_all_reduce_buffer_bytes",
     "b200q_all_reduce",
+    "b200q_marlin_gemm_all_reduce",
 )
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4
@@ -76,17 +76,20 @@ def load() -> ctypes.CDLL:
     lib.b200q_marlin_gemm.argtypes = [
         vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, c.c_size_t, vp, i64, i64, i32,
         i64, i64, i64, i64, u32, vp]
+    lib.b200q_marlin_gemm_all_reduce.restype = i32
+    lib.b200q_marlin_gemm_all_reduce.argtypes = [
+        vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, c.c_size_t, vp, i64, i64, i32,
+        i64, i64, i64, i64, u32, vp, vp, i32, i32, i64, vp]
     lib.b200q_marlin_gemm_noalloc_max_scratch.restype = c.c_size_t
     lib.b200q_marlin_gemm_noalloc_max_scratch.argtypes = []
     lib.b200q_marlin_gemm_noalloc.restype = i32
     lib.b200q_marlin_gemm_noalloc.argtypes = [
         vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i64, i64, i64, i64, u32, vp]
-    lib.b200q_all_reduce_flag_bytes.restype = c.c_size_t
-    lib.b200q_all_reduce_epoch_bytes.restype = c.c_size_t
+    lib.b200q_all_reduce_state_bytes.restype = c.c_size_t
     lib.b200q_all_reduce.restype = i32
     lib.b200q_all_reduce_buffer_bytes.restype = c.c_size_t
     lib.b200q_all_reduce_buffer_bytes.argtypes = [i32, i64]
-    lib.b200q_all_reduce.argtypes = [vp, vp, vp, i32, i32, i64, vp, vp, i64, i32, vp]
+    lib.b200q_all_reduce.argtypes = [vp, vp, i32, i32, i64, vp, vp, i64, i32, vp]
     _lib = lib
     return lib
 

@@ -132,14 +132,31 @@ extern "C" size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n
   return (size_t)bytes;
 }
 
-extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q_weight,
-                                 const void* b_scales, const uint32_t* b_zeros,
-                                 const int32_t* g_idx, const int32_t* perm, const void* b_bias,
-                                 void* c, void* scratch, size_t scratch_bytes, int32_t* workspace,
-                                 int64_t workspace_len, int64_t b_q_type_id, int a_dtype,
-                                 int64_t size_m, int64_t size_n, int64_t size_k,
-                                 int64_t num_groups, unsigned flags, b200q_stream_t stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+namespace b200q {
+int launch_all_reduce(const ArLink& link, const void* in, void* out, int64_t n_elems, int dtype,
+                      cudaStream_t stream);
+int check_link(void* const* peer_bufs, uint32_t* state, int rank, int world,
+               int64_t max_message_bytes, ArLink* link);
+}  // namespace b200q
+
+// B200Q_NO_FUSED_AR=1: always the stand-alone all-reduce kernel (debugging aid).
+static bool fused_ar_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B200Q_NO_FUSED_AR");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
+// The GEMM behind both entry points.  With `link` the output is all-reduced over the
+// peer link: inside the GEMM kernel where one decode launch covers the problem,
+// otherwise by the stand-alone kernel on the finished output.
+static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, const void* b_scales,
+                     const uint32_t* b_zeros, const int32_t* g_idx, const int32_t* perm,
+                     const void* b_bias, void* c, void* scratch, size_t scratch_bytes,
+                     int32_t* workspace, int64_t workspace_len, int64_t b_q_type_id, int a_dtype,
+                     int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups,
+                     unsigned flags, cudaStream_t stream, const ArLink* link) {
   // ---- type contract ---------------------------------------------------------------
   int bits = 0;
   bool type_has_zp = false;
@@ -243,9 +260,14 @@ extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q
   }
 
   // ---- prefill regime: tensor-core kernel ----------------------------------------------
-  if (tc_path_enabled() && group_blocks >= 2 && tc_gemm_supported(size_m, size_n, size_k, gm))
-    return launch_tc_gemm(a_used, lda_used, b_q_weight, b_scales, b_zeros, b_bias, c, a_dtype, bits,
-                          size_m, size_n, size_k, group_blocks, gm == kChannel, stream);
+  if (tc_path_enabled() && group_blocks >= 2 && tc_gemm_supported(size_m, size_n, size_k, gm)) {
+    int rc = launch_tc_gemm(a_used, lda_used, b_q_weight, b_scales, b_zeros, b_bias, c, a_dtype,
+                            bits, size_m, size_n, size_k, group_blocks, gm == kChannel, stream);
+    if (rc != B200Q_OK || !link) return rc;
+    return launch_all_reduce(*link, c, c, size_m * size_n, a_dtype, stream);
+  }
+  // one decode launch of the streaming kernel covers the problem: it all-reduces itself
+  const bool fuse_ar = link && size_m <= 32 && gm != kLookup && fused_ar_enabled();
 
   // ---- decode regime: chunks of up to 64 rows --------------------------------------------
   const int nt = (int)(size_n / 64);
@@ -278,6 +300,8 @@ extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q
     p.slices = nt / ntw;
     p.group_blocks = group_blocks;
     p.num_groups = (int)num_groups;
+    p.ar = ArLink{};
+    if (fuse_ar) p.ar = *link;
     int rc;
     if (a_dtype == B200Q_F16) {
       rc = bits == 4 ? dispatch_stream<half, 4>(p, has_zp, gm, mb, ntw, (int)max_ctas, stream)
@@ -292,5 +316,35 @@ extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q
                 (long long)size_n, (long long)size_k);
     if (rc != B200Q_OK) return rc;
   }
+  if (link && !fuse_ar) return launch_all_reduce(*link, c, c, size_m * size_n, a_dtype, stream);
   return B200Q_OK;
+}
+
+extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q_weight,
+                                 const void* b_scales, const uint32_t* b_zeros,
+                                 const int32_t* g_idx, const int32_t* perm, const void* b_bias,
+                                 void* c, void* scratch, size_t scratch_bytes, int32_t* workspace,
+                                 int64_t workspace_len, int64_t b_q_type_id, int a_dtype,
+                                 int64_t size_m, int64_t size_n, int64_t size_k,
+                                 int64_t num_groups, unsigned flags, b200q_stream_t stream) {
+  return gemm_impl(a, lda, b_q_weight, b_scales, b_zeros, g_idx, perm, b_bias, c, scratch,
+                   scratch_bytes, workspace, workspace_len, b_q_type_id, a_dtype, size_m, size_n,
+                   size_k, num_groups, flags, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+extern "C" int b200q_marlin_gemm_all_reduce(
+    const void* a, int64_t lda, const uint32_t* b_q_weight, const void* b_scales,
+    const uint32_t* b_zeros, const int32_t* g_idx, const int32_t* perm, const void* b_bias, void* c,
+    void* scratch, size_t scratch_bytes, int32_t* workspace, int64_t workspace_len,
+    int64_t b_q_type_id, int a_dtype, int64_t size_m, int64_t size_n, int64_t size_k,
+    int64_t num_groups, unsigned flags, void* const* peer_bufs, uint32_t* state, int rank, int world, int64_t max_message_bytes, b200q_stream_t stream) {
+  ArLink link;
+  int rc = check_link(peer_bufs, state, rank, world, max_message_bytes, &link);
+  if (rc != B200Q_OK) return rc;
+  B200Q_REQUIRE(size_m >= 0 && size_n >= 0 && size_m * size_n * 2 <= max_message_bytes,
+                B200Q_EINVAL, "output of %lld x %lld exceeds the slot size %lld",
+                (long long)size_m, (long long)size_n, (long long)max_message_bytes);
+  return gemm_impl(a, lda, b_q_weight, b_scales, b_zeros, g_idx, perm, b_bias, c, scratch,
+                   scratch_bytes, workspace, workspace_len, b_q_type_id, a_dtype, size_m, size_n,
+                   size_k, num_groups, flags, static_cast<cudaStream_t>(stream), &link);
 }

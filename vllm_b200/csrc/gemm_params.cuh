@@ -1,6 +1,7 @@
 // Parameter block and constants shared by the decode-regime GEMM kernels.
 #pragma once
 
+#include "ar_link.cuh"
 #include "common.cuh"
 
 namespace b200q {
@@ -29,6 +30,8 @@ struct StreamParams {
   int num_groups;
   // weight-embedding constants of the streaming kernel (filled by its launcher)
   uint32_t c_ex, c_mask_lo, c_mask_hi;
+  // when ar.world > 0 the streaming kernel all-reduces its output over the link
+  ArLink ar;
 };
 
 constexpr int kStreamWarps = 8;

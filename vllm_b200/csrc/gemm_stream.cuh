@@ -574,7 +574,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
 
     // ---- cross-CTA reduction inside the cluster, through distributed shared memory ----
     // Every CTA publishes its tile in its own shared memory; after a cluster
-    // barrier the rows of the tile are shared out among the CTAs (row % ksplit),
+    // barrier the 8-row blocks of the tile are shared out among the CTAs (block % ksplit),
     // and each sums the ranks' copies in rank order (bitwise reproducible).
     bool do_store = true;
     if (ksplit > 1) {
@@ -592,7 +592,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         const int row = i * 8 + o_row;
-        if ((uint32_t)row % ksplit == krank) {
+        if ((uint32_t)i % ksplit == krank) {
           do_store = true;
 #pragma unroll
           for (int e = 0; e < Cfg::kEpt; ++e) outv[i][e] = 0.f;
@@ -620,9 +620,17 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
       }
     }
 
-    // ---- epilogue: channel scale, bias, convert, store -----------------------------
+    // no CTA may exit while others still read its shared memory; after this barrier
+    // CTAs without output rows leave at once and make room for the next kernel
+    if (ksplit > 1) {
+      asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    }
+
+    // ---- epilogue: channel scale, bias, convert, store (or all-reduce) ---------------
+    const int n_base = nt0 * 64 + o_col;
+    uint32_t packed[MT][Cfg::kEpt / 2];
     if (do_store) {
-      const int n_base = nt0 * 64 + o_col;
       float cs[Cfg::kEpt], bs[Cfg::kEpt];
 #pragma unroll
       for (int e = 0; e < Cfg::kEpt; ++e) {
@@ -631,31 +639,90 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
                              static_cast<const uint16_t*>(p.bias)[single_perm_pos(n_base + e)])
                        : 0.f;
       }
-      uint16_t* C = static_cast<uint16_t*>(p.c);
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
-        const int row = i * 8 + o_row;
-        if (row < p.m && (ksplit == 1 || (uint32_t)row % ksplit == krank)) {
-          uint32_t packed[Cfg::kEpt / 2];
 #pragma unroll
-          for (int e = 0; e < Cfg::kEpt; e += 2) {
-            const float v0 = outv[i][e] * cs[e] + bs[e];
-            const float v1 = outv[i][e + 1] * cs[e + 1] + bs[e + 1];
-            packed[e / 2] =
-                (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
-          }
-          uint16_t* dst = C + (size_t)row * p.n + n_base;
-          if constexpr (Cfg::kEpt == 4)
-            *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[1]);
-          else
-            *reinterpret_cast<uint32_t*>(dst) = packed[0];
+        for (int e = 0; e < Cfg::kEpt; e += 2) {
+          const float v0 = outv[i][e] * cs[e] + bs[e];
+          const float v1 = outv[i][e + 1] * cs[e + 1] + bs[e + 1];
+          packed[i][e / 2] =
+              (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
         }
       }
     }
-    // no CTA may exit while others still read its shared memory
-    if (ksplit > 1) {
-      asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-      asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    auto blk_mine = [&](int i) {
+      return do_store && i * 8 + o_row < p.m && (ksplit == 1 || (uint32_t)i % ksplit == krank);
+    };
+    if (p.ar.world == 0) {
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        if (!blk_mine(i)) continue;
+        uint16_t* dst = static_cast<uint16_t*>(p.c) + (size_t)(i * 8 + o_row) * p.n + n_base;
+        if constexpr (Cfg::kEpt == 4)
+          *reinterpret_cast<uint2*>(dst) = make_uint2(packed[i][0], packed[i][1]);
+        else
+          *reinterpret_cast<uint32_t*>(dst) = packed[i][0];
+      }
+    } else {
+      // All-reduce over the peer link (protocol in ar_link.cuh): the rounded partial of
+      // this rank goes to every peer as flagged packets, each thread then collects the
+      // peers' packets for its own elements and sums in rank order.
+      const ArLink& l = p.ar;
+      const uint32_t call = ar_ld_volatile(l.state);
+      const uint32_t flag = ar_flag(call);
+      const long long parity_off = (long long)(call & 1) * l.world * l.slot_bytes;
+      for (int r = 0; r < l.world; ++r) {
+        if (r == l.rank) continue;
+        char* slot = static_cast<char*>(l.bufs[r]) + parity_off + l.rank * l.slot_bytes;
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+          if (!blk_mine(i)) continue;
+          char* dst = slot + ((size_t)(i * 8 + o_row) * p.n + n_base) * 4;  // 2 values per 8 B
+          if constexpr (Cfg::kEpt == 4)
+            ar_put2(dst, packed[i][0], packed[i][1], flag);
+          else
+            ar_put1(dst, packed[i][0], flag);
+        }
+      }
+      const char* mybuf = static_cast<const char*>(l.bufs[l.rank]) + parity_off;
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        if (!blk_mine(i)) continue;
+        const size_t el = (size_t)(i * 8 + o_row) * p.n + n_base;
+        float sum[Cfg::kEpt];
+#pragma unroll
+        for (int e = 0; e < Cfg::kEpt; ++e) sum[e] = 0.f;
+        bool ok = true;
+        for (int r = 0; r < l.world; ++r) {
+          uint32_t v[2] = {packed[i][0], Cfg::kEpt == 4 ? packed[i][Cfg::kEpt / 2 - 1] : 0u};
+          if (r != l.rank) {
+            const char* src = mybuf + r * l.slot_bytes + el * 4;
+            ok = (Cfg::kEpt == 4) ? ar_get2(src, flag, v[0], v[1]) : ar_get1(src, flag, v[0]);
+            if (!ok) {
+              atomicCAS(l.error, 0, 0x100 | r);
+              break;
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < Cfg::kEpt / 2; ++e) {
+            sum[2 * e] += Pair<T>::to_float((uint16_t)(v[e] & 0xffffu));
+            sum[2 * e + 1] += Pair<T>::to_float((uint16_t)(v[e] >> 16));
+          }
+        }
+        if (!ok) break;
+        uint32_t o[2];
+#pragma unroll
+        for (int e = 0; e < Cfg::kEpt / 2; ++e)
+          o[e] = (uint32_t)Pair<T>::from_float(sum[2 * e]) |
+                 ((uint32_t)Pair<T>::from_float(sum[2 * e + 1]) << 16);
+        uint16_t* dst = static_cast<uint16_t*>(p.c) + el;
+        if constexpr (Cfg::kEpt == 4)
+          *reinterpret_cast<uint2*>(dst) = make_uint2(o[0], o[1]);
+        else
+          *reinterpret_cast<uint32_t*>(dst) = o[0];
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) ar_arrive(l, call, gridDim.x);
     }
   }
 }

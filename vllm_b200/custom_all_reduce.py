@@ -18,6 +18,40 @@ import torch.distributed as dist
 from . import _lib
 
 
+class FusedReduceScope:
+    """While active, the next quantized GEMM issued through ``gptq_marlin_gemm`` all-reduces
+    its own output over the peer link (``b200q_marlin_gemm_all_reduce``) when the output fits
+    a slot; ``done`` tells the caller whether that happened."""
+
+    def __init__(self, car: "CustomAllreduce | None") -> None:
+        self.car = car if (car is not None and not car.disabled) else None
+        self.done = False
+
+    def __enter__(self) -> "FusedReduceScope":
+        global _ACTIVE_SCOPE
+        self._outer, _ACTIVE_SCOPE = _ACTIVE_SCOPE, (self if self.car is not None else None)
+        return self
+
+    def __exit__(self, *exc) -> None:
+        global _ACTIVE_SCOPE
+        _ACTIVE_SCOPE = self._outer
+
+    def accepts(self, c: torch.Tensor) -> bool:
+        return not self.done and self.car.should_custom_ar(c)
+
+    def link_args(self) -> tuple:
+        car, vp = self.car, ctypes.c_void_p
+        return (vp(car.data_hdl.buffer_ptrs_dev), vp(car.state.data_ptr()), car.rank,
+                car.world_size, car.max_size)
+
+
+_ACTIVE_SCOPE: FusedReduceScope | None = None
+
+
+def active_scope() -> FusedReduceScope | None:
+    return _ACTIVE_SCOPE
+
+
 class CustomAllreduce:
     # messages above this go to NCCL (the reference caps its one-stage kernel at 256-512 KiB,
     # csrc/custom_all_reduce.cuh:592-593, and the whole path at 1-2 MiB on compute capability 10.0)
@@ -35,15 +69,12 @@ class CustomAllreduce:
         symm_mem.enable_symm_mem_for_group(group.group_name)
         self.data = symm_mem.empty(self.lib.b200q_all_reduce_buffer_bytes(self.world_size, max_size),
                                    dtype=torch.uint8, device=device)
+        self.data.zero_()                  # flag 0 marks a packet that was never written
         self.data_hdl = symm_mem.rendezvous(self.data, group.group_name)
-        nflag = self.lib.b200q_all_reduce_flag_bytes() // 4
-        self.flags = symm_mem.empty(nflag, dtype=torch.int32, device=device)
-        self.flags.zero_()
-        self.flags_hdl = symm_mem.rendezvous(self.flags, group.group_name)
-        self.epochs = torch.zeros(self.lib.b200q_all_reduce_epoch_bytes() // 4, dtype=torch.int32,
-                                  device=device)
+        self.state = torch.zeros(self.lib.b200q_all_reduce_state_bytes() // 4, dtype=torch.int32,
+                                 device=device)
         torch.cuda.synchronize(device)
-        dist.barrier(group=group)          # every rank's flags are zero before anyone signals
+        dist.barrier(group=group)          # every rank's buffer is zero before anyone sends
         self.disabled = False
 
     def should_custom_ar(self, inp: torch.Tensor) -> bool:
@@ -61,8 +92,8 @@ class CustomAllreduce:
         out = torch.empty_like(inp)
         vp = ctypes.c_void_p
         rc = self.lib.b200q_all_reduce(
-            vp(self.data_hdl.buffer_ptrs_dev), vp(self.flags_hdl.buffer_ptrs_dev),
-            vp(self.epochs.data_ptr()), self.rank, self.world_size, self.max_size,
+            vp(self.data_hdl.buffer_ptrs_dev), vp(self.state.data_ptr()), self.rank,
+            self.world_size, self.max_size,
             vp(inp.data_ptr()), vp(out.data_ptr()), inp.numel(),
             _lib.BF16 if inp.dtype == torch.bfloat16 else _lib.F16,
             vp(torch.cuda.current_stream(self.device).cuda_stream))

@@ -45,6 +45,13 @@ def enable_custom_all_reduce(device: torch.device, max_size: int = 1 << 19) -> b
     return not _CUSTOM_AR.disabled
 
 
+def fused_all_reduce_scope():
+    """Context for a row-parallel layer: the quantized GEMM issued inside it all-reduces its own
+    output when the peer link is up and the output fits (see FusedReduceScope)."""
+    from .custom_all_reduce import FusedReduceScope
+    return FusedReduceScope(_CUSTOM_AR)
+
+
 def destroy_model_parallel() -> None:
     global _TP_GROUP, _TP_RANK, _TP_SIZE, _CUSTOM_AR
     _TP_GROUP, _TP_RANK, _TP_SIZE, _CUSTOM_AR = None, 0, 1, None

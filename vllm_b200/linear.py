@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from .distributed import (divide, get_tensor_model_parallel_rank,
+from .distributed import (divide, fused_all_reduce_scope, get_tensor_model_parallel_rank,
                           get_tensor_model_parallel_world_size, tensor_model_parallel_all_gather,
                           tensor_model_parallel_all_reduce)
 from .parameter import ShardedParameter
@@ -167,7 +167,11 @@ class RowParallelLinear(LinearBase):
         if not self.input_is_parallel and self.tp_size > 1:
             input_ = input_.chunk(self.tp_size, dim=-1)[self.tp_rank].contiguous()
         bias = self.bias if (self.tp_rank == 0 or self.tp_size == 1) else None
-        out = self.quant_method.apply(self, input_, bias)
-        if self.reduce_results and self.tp_size > 1:
-            out = all_reduce(out)
-        return out
+        if not (self.reduce_results and self.tp_size > 1):
+            return self.quant_method.apply(self, input_, bias)
+        if all_reduce is not tensor_model_parallel_all_reduce:
+            return all_reduce(self.quant_method.apply(self, input_, bias))
+        # GEMM -> all-reduce is one kernel where the peer link is up and the output is small
+        with fused_all_reduce_scope() as scope:
+            out = self.quant_method.apply(self, input_, bias)
+        return out if scope.done else all_reduce(out)
