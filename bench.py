@@ -226,7 +226,8 @@ def run_ours(args, world, rank, local_rank):
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     pools = [LayerPool(torch, dev, dt, *layer, gen) for layer in LAYERS]
     ws = mu.marlin_make_workspace_new(dev)
-    max_scratch = max(lib.b200q_marlin_gemm_scratch_bytes(max(MS), p.n, p.k, 1) for p in pools)
+    max_scratch = max(lib.b200q_marlin_gemm_preferred_scratch_bytes(m, p.n, p.k, 1)
+                      for p in pools for m in MS)
     scratch = torch.empty(max_scratch, dtype=torch.uint8, device=dev)
     a_dev = {(p.k, m): torch.randn((m, p.k), device=dev, dtype=dt, generator=gen)
              for p in pools for m in MS}

@@ -107,6 +107,15 @@ size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n,
                                        int64_t size_k, int has_act_order);
 
 /*
+ * Scratch size with which b200q_marlin_gemm runs fastest: the size above plus room
+ * for the fp32 partial sums of the tensor-core kernel's k-split (used when a
+ * problem has fewer output tiles than the GPU has SMs; at most 64 MiB).  Any size
+ * between the two is accepted: the split shrinks to what the scratch holds.
+ */
+size_t b200q_marlin_gemm_preferred_scratch_bytes(int64_t size_m, int64_t size_n,
+                                                 int64_t size_k, int has_act_order);
+
+/*
  * C[M,N] = A[M,K] * dequant(B) (+ bias): the mixed-precision GEMM.
  * Replaces: gptq_marlin_gemm, csrc/quantization/gptq_marlin/gptq_marlin.cu:674-959
  *           (op schema csrc/torch_bindings.cpp:308-315).

@@ -275,7 +275,8 @@ def _gptq_marlin_gemm_cuda(a, c_or_none, b_q_weight, b_bias_or_none, b_scales, g
         sms = _L.b200q_sm_count()
         _check(workspace.numel() >= sms,
                f"workspace.numel = {workspace.numel()} is below min_workspace_size = {sms}")
-        nbytes = _L.b200q_marlin_gemm_scratch_bytes(size_m, size_n, size_k, int(g_idx is not None))
+        nbytes = _L.b200q_marlin_gemm_preferred_scratch_bytes(size_m, size_n, size_k,
+                                                             int(g_idx is not None))
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=a.device)
         flags = ((_lib.FLAG_K_FULL if is_k_full else 0)
                  | (_lib.FLAG_ATOMIC_ADD if use_atomic_add else 0)

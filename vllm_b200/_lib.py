@@ -22,6 +22,7 @@ EXPORTS = (
     "b200q_awq_marlin_repack",
     "b200q_permute_cols",
     "b200q_marlin_gemm_scratch_bytes",
+    "b200q_marlin_gemm_preferred_scratch_bytes",
     "b200q_marlin_gemm",
     "b200q_marlin_gemm_noalloc_max_scratch",
     "b200q_marlin_gemm_noalloc",
@@ -72,6 +73,8 @@ def load() -> ctypes.CDLL:
     lib.b200q_permute_cols.argtypes = [vp, i64, vp, vp, i64, i64, vp]
     lib.b200q_marlin_gemm_scratch_bytes.restype = c.c_size_t
     lib.b200q_marlin_gemm_scratch_bytes.argtypes = [i64, i64, i64, i32]
+    lib.b200q_marlin_gemm_preferred_scratch_bytes.restype = c.c_size_t
+    lib.b200q_marlin_gemm_preferred_scratch_bytes.argtypes = [i64, i64, i64, i32]
     lib.b200q_marlin_gemm.restype = i32
     lib.b200q_marlin_gemm.argtypes = [
         vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, c.c_size_t, vp, i64, i64, i32,

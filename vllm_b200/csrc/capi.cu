@@ -65,7 +65,8 @@ bool tc_gemm_supported(int64_t size_m, int64_t size_n, int64_t size_k, int gm);
 int launch_tc_gemm(const void* a, int64_t lda, const uint32_t* b, const void* scales,
                    const uint32_t* zeros, const void* bias, void* c, int a_dtype, int bits,
                    int64_t size_m, int64_t size_n, int64_t size_k, int group_blocks,
-                   int channelwise, cudaStream_t stream);
+                   int channelwise, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
+int64_t tc_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k);
 int tc_error_flag(bool reset);
 int ar_error_flag(bool reset);
 
@@ -109,6 +110,13 @@ int64_t partial_bytes(int64_t size_n) {
   return (kMaxGrid + nt) * 64 * 64 * 4;
 }
 
+// first region of the scratch: decode partial sums or the tensor-core kernel's k-split partials
+int64_t work_bytes(int64_t size_m, int64_t size_n, int64_t size_k) {
+  const int64_t tc = tc_path_enabled() ? tc_gemm_scratch_bytes(size_m, size_n, size_k) : 0;
+  const int64_t dec = partial_bytes(size_n);
+  return align_up(tc > dec ? tc : dec, 256);
+}
+
 }  // namespace
 }  // namespace b200q
 
@@ -128,6 +136,14 @@ extern "C" size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n
                                                   int has_act_order) {
   if (size_m <= 0 || size_n <= 0 || size_k <= 0) return 256;
   int64_t bytes = align_up(partial_bytes(size_n), 256);
+  if (has_act_order) bytes += align_up(size_m * size_k * 2, 256);
+  return (size_t)bytes;
+}
+
+extern "C" size_t b200q_marlin_gemm_preferred_scratch_bytes(int64_t size_m, int64_t size_n,
+                                                            int64_t size_k, int has_act_order) {
+  if (size_m <= 0 || size_n <= 0 || size_k <= 0) return 256;
+  int64_t bytes = work_bytes(size_m, size_n, size_k);
   if (has_act_order) bytes += align_up(size_m * size_k * 2, 256);
   return (size_t)bytes;
 }
@@ -241,6 +257,8 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
   }
 
   // ---- scratch -----------------------------------------------------------------------
+  // the k-split of the tensor-core kernel is optional: it shrinks to what the scratch holds
+  const int64_t a_tmp_bytes = has_act_order ? align_up(size_m * size_k * 2, 256) : 0;
   const size_t need = b200q_marlin_gemm_scratch_bytes(size_m, size_n, size_k, has_act_order);
   B200Q_REQUIRE(scratch && scratch_bytes >= need, B200Q_ESCRATCH,
                 "scratch of %zu bytes is below the required %zu", scratch_bytes, need);
@@ -252,7 +270,7 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
   if (has_act_order) {
     // gather the activation columns into sorted-row order once
     // (gptq_marlin.cu:549-564); the GEMM then reads a contiguous matrix
-    void* a_tmp = static_cast<char*>(scratch) + align_up(partial_bytes(size_n), 256);
+    void* a_tmp = static_cast<char*>(scratch) + (scratch_bytes - a_tmp_bytes) / 256 * 256;
     int rc = launch_permute_cols(a, lda, perm, a_tmp, size_m, size_k, stream);
     if (rc != B200Q_OK) return rc;
     a_used = a_tmp;
@@ -262,7 +280,8 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
   // ---- prefill regime: tensor-core kernel ----------------------------------------------
   if (tc_path_enabled() && group_blocks >= 2 && tc_gemm_supported(size_m, size_n, size_k, gm)) {
     int rc = launch_tc_gemm(a_used, lda_used, b_q_weight, b_scales, b_zeros, b_bias, c, a_dtype,
-                            bits, size_m, size_n, size_k, group_blocks, gm == kChannel, stream);
+                            bits, size_m, size_n, size_k, group_blocks, gm == kChannel, scratch,
+                            (int64_t)((scratch_bytes - a_tmp_bytes) / 256 * 256), stream);
     if (rc != B200Q_OK || !link) return rc;
     return launch_all_reduce(*link, c, c, size_m * size_n, a_dtype, stream);
   }

@@ -44,6 +44,7 @@ constexpr int kEpiWarp0 = kDequantWarps;           // 4 warps: TMEM lane quadran
 constexpr int kProducerWarp = kEpiWarp0 + 4;
 constexpr int kMmaWarp = kProducerWarp + 1;
 constexpr int kThreads = 32 * (kMmaWarp + 1);
+constexpr int64_t kMaxSplitBytes = 64ll << 20;  // cap on the fp32 partials of a k-split
 constexpr uint32_t kSpinLimit = 1u << 24;   // polls; each poll may sleep up to kSuspendNs
 constexpr uint32_t kSuspendNs = 1000;       // try_wait suspend-time hint: pollers leave the issue slots alone
 
@@ -60,6 +61,10 @@ struct TcParams {
   int m, n, k;
   int group_blocks;       // k-tiles (16 rows) per scale group; K/16 when there is one group
   int channelwise;        // scales use the 32-column "single" permutation
+  // split-K: a tile's k-range is shared by `ksplit` work items; each leaves fp32 partial
+  // sums in `partials`, which splitk_reduce_kernel adds up in split order afterwards
+  int ksplit;
+  float* partials;        // [tiles * ksplit][BM][BN] fp32
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------
@@ -233,6 +238,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
   auto stage_s = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kSOff; };
   auto stage_z = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kZOff; };
 
+  // a k-split's reduce kernel may be scheduled while this kernel runs (it waits for
+  // this kernel's completion itself)
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   __shared__ int s_abort;
   volatile int* cta_abort = &s_abort;
   const int warp = threadIdx.x >> 5;
@@ -241,6 +249,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
   const int n_tiles = (p.n + BN - 1) / BN;
   const int total_tiles = m_tiles * n_tiles;
   const int kb_total = p.k / kBK;
+  const int KS = p.ksplit;
+  const int total_items = total_tiles * KS;  // work item = (tile, share of the k-range)
   const int NT = p.n / 64;  // 64-column Marlin tiles
   const int gb = p.group_blocks;
 
@@ -272,11 +282,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
       int st_i = 0;
       uint32_t st_ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const int t = item / KS, ks = item - t * KS;
+        const int kb0 = (int)((long long)kb_total * ks / KS);
+        const int kb1 = (int)((long long)kb_total * (ks + 1) / KS);
         const int tn = t / m_tiles, tm = t % m_tiles;
         const int nt0 = tn * NTT;
         const int nt_valid = min(NTT, NT - nt0);
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = st_i;
           const uint32_t ph = st_ph;
           if (++st_i == S) { st_i = 0; st_ph ^= 1; }
@@ -316,12 +329,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
       int st_i = 0;
       uint32_t st_ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++tile_i) {
+        const int ks = item % KS;
+        const int kb0 = (int)((long long)kb_total * ks / KS);
+        const int kb1 = (int)((long long)kb_total * (ks + 1) / KS);
         const int buf = Cfg::kBufs == 2 ? (tile_i & 1) : 0;
         const uint32_t bph = Cfg::kBufs == 2 ? ((tile_i >> 1) & 1) : (tile_i & 1);
         if (!(ok = mbar_wait(tmem_empty(buf), bph ^ 1, (2 << 8) | 5, cta_abort))) break;
         tc_fence_after();
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = st_i;
           const uint32_t ph = st_ph;
           if (++st_i == S) { st_i = 0; st_ph ^= 1; }
@@ -335,7 +351,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
             const uint64_t db = smem_desc_sw128(stage_b(s));
 #pragma unroll
             for (int k16 = 0; k16 < kBK / 16; ++k16)
-              umma_f16(d, da + 2 * k16, db + 2 * k16, idesc, (kb | k16) != 0);
+              umma_f16(d, da + 2 * k16, db + 2 * k16, idesc, (kb > kb0) || (k16 != 0));
           }
           umma_commit(empty(s));  // stage reusable once these MMAs have read it
         }
@@ -372,11 +388,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     int st_i = 0;
     uint32_t st_ph = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int t = item / KS, ks = item - t * KS;
+      const int kb0 = (int)((long long)kb_total * ks / KS);
+      const int kb1 = (int)((long long)kb_total * (ks + 1) / KS);
       const int tn = t / m_tiles;
       const int nt0 = tn * NTT;
       const int nt_valid = min(NTT, NT - nt0);
-      for (int kb = 0; kb < kb_total; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = st_i;
         const uint32_t ph = st_ph;
         if (++st_i == S) { st_i = 0; st_ph ^= 1; }
@@ -497,7 +516,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     uint16_t* C = static_cast<uint16_t*>(p.c);
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_i) {
+    // bias, rounding and the store of 16 consecutive columns of one row
+    auto store16 = [&](int row, int n0, const float (&v)[16]) {
+      uint32_t packed[8];
+#pragma unroll
+      for (int e = 0; e < 16; e += 2) {
+        float v0 = v[e], v1 = v[e + 1];
+        if (bias) {
+          v0 += Pair<T>::to_float(bias[single_perm_pos(n0 + e)]);
+          v1 += Pair<T>::to_float(bias[single_perm_pos(n0 + e + 1)]);
+        }
+        packed[e / 2] =
+            (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(C + (size_t)row * p.n + n0);
+      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    };
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++tile_i) {
+      const int t = item / KS, ks = item - t * KS;
       const int tn = t / m_tiles, tm = t % m_tiles;
       const int buf = Cfg::kBufs == 2 ? (tile_i & 1) : 0;
       const uint32_t bph = Cfg::kBufs == 2 ? ((tile_i >> 1) & 1) : (tile_i & 1);
@@ -505,7 +542,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
       tc_fence_after();
 #pragma unroll
       for (int h = 0; h < Cfg::kAccs; ++h) {
-        const int row = tm * BM + h * 128 + quad * 32 + lane;
+        const int trow = h * 128 + quad * 32 + lane;  // row inside the tile
+        const int row = tm * BM + trow;
+        float* part = p.partials + ((size_t)item * BM + trow) * BN;
 #pragma unroll 1
         for (int cb = 0; cb < BN / 32; ++cb) {
           uint32_t r[32];
@@ -514,22 +553,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
           tmem_ld_wait();
           const int n0 = tn * BN + cb * 32;
           if (row < p.m && n0 < p.n) {
-            uint32_t packed[16];
+            if (KS == 1) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              float v0 = __uint_as_float(r[e]), v1 = __uint_as_float(r[e + 1]);
-              if (bias) {
-                v0 += Pair<T>::to_float(bias[single_perm_pos(n0 + e)]);
-                v1 += Pair<T>::to_float(bias[single_perm_pos(n0 + e + 1)]);
+              for (int hh = 0; hh < 2; ++hh) {
+                float v[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[16 * hh + e]);
+                store16(row, n0 + 16 * hh, v);
               }
-              packed[e / 2] =
-                  (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(C + (size_t)row * p.n + n0);
+            } else {
+              float4* dst = reinterpret_cast<float4*>(part + cb * 32);
 #pragma unroll
-            for (int v = 0; v < 4; ++v)
-              dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2],
-                                  packed[4 * v + 3]);
+              for (int v4 = 0; v4 < 8; ++v4)
+                __stcg(dst + v4, make_float4(__uint_as_float(r[4 * v4]), __uint_as_float(r[4 * v4 + 1]),
+                                             __uint_as_float(r[4 * v4 + 2]),
+                                             __uint_as_float(r[4 * v4 + 3])));
+            }
           }
         }
       }
@@ -545,6 +584,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+}
+
+// Sum of a k-split's partials in split order, bias, rounding: one thread per row and
+// eight consecutive columns.
+template <typename T>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partials, const void* __restrict__ bias_, void* c,
+                     int m, int n, int bm, int bn, int ks) {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  const int n8 = n / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)m * n8) return;
+  const int row = (int)(idx / n8), n0 = (int)(idx % n8) * 8;
+  const int m_tiles = (m + bm - 1) / bm;
+  const int t = (n0 / bn) * m_tiles + row / bm;
+  const float* src = partials + ((size_t)t * ks * bm + row % bm) * bn + n0 % bn;
+  const size_t split_stride = (size_t)bm * bn;
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = 0.f;
+  for (int s2 = 0; s2 < ks; ++s2) {
+    const float4 x0 = __ldcg(reinterpret_cast<const float4*>(src + s2 * split_stride));
+    const float4 x1 = __ldcg(reinterpret_cast<const float4*>(src + s2 * split_stride) + 1);
+    v[0] += x0.x; v[1] += x0.y; v[2] += x0.z; v[3] += x0.w;
+    v[4] += x1.x; v[5] += x1.y; v[6] += x1.z; v[7] += x1.w;
+  }
+  const uint16_t* bias = static_cast<const uint16_t*>(bias_);
+  uint32_t packed[4];
+#pragma unroll
+  for (int e = 0; e < 8; e += 2) {
+    float v0 = v[e], v1 = v[e + 1];
+    if (bias) {
+      v0 += Pair<T>::to_float(bias[single_perm_pos(n0 + e)]);
+      v1 += Pair<T>::to_float(bias[single_perm_pos(n0 + e + 1)]);
+    }
+    packed[e / 2] = (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
+  }
+  *reinterpret_cast<uint4*>(static_cast<uint16_t*>(c) + (size_t)row * n + n0) =
+      make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
 // ---- host side ----------------------------------------------------------------------
@@ -602,12 +680,27 @@ static int launch_one(const CUtensorMap& map, const TcParams& p, cudaStream_t st
                                        Cfg::kSmemBytes));
     attr_done[dev & 63] = true;
   }
-  const int tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
+  const int items = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.ksplit;
   const int sms = device_sm_count();
-  const int grid = tiles < sms ? tiles : sms;
+  const int grid = items < sms ? items : sms;
   kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map, b_map, p);
   note_launch();
   B200Q_CUDA_OK(cudaGetLastError());
+  if (p.ksplit > 1) {
+    const long long threads = (long long)p.m * (p.n / 8);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<T>, (const float*)p.partials, p.bias,
+                                     p.c, p.m, p.n, BM, BN, p.ksplit));
+    note_launch();
+  }
   return B200Q_OK;
 }
 
@@ -628,23 +721,47 @@ static int launch_bits(const CUtensorMap& map, const TcParams& p, bool has_zp, i
                 : launch_tile<T, BITS, false>(map, p, bm, bn, stream);
 }
 
-// Tile shape for a problem: least estimated time = waves * tile area / efficiency,
-// with the relative efficiencies measured on B200 at M = 4096 (the dequant warps'
-// time per k-step is nearly constant, so tiles with more MMA work per converted
-// column run closer to the tensor-pipe rate).
-static void choose_tile(int64_t m, int64_t n, int bits, int sms, int* bm_out, int* bn_out) {
-  (void)bits;
-  static const struct { int bm, bn; double eff; } kCand[4] = {
-      {256, 256, 1.00}, {256, 128, 0.72}, {128, 256, 0.65}, {128, 128, 0.50}};
-  double best = 1e300;
+// Tile shape and k-split for a problem: least estimated time.  A work item takes
+// (its k-steps + a fixed fill / drain cost) x the time of one k-step of the tile
+// shape; the relative step times were measured on B200 (the dequant warps' time per
+// k-step is nearly constant, so tiles with more MMA work per converted column run
+// closer to the tensor-pipe rate; small tiles are bound by the latency of the stage
+// ring).  Splitting K pays when there are fewer tiles than SMs; it costs one more
+// launch and the fp32 partial traffic.  `scratch_bytes` bounds the partials.
+struct TcPlan {
+  int bm, bn, ksplit;
+  int64_t partial_bytes;
+};
+static TcPlan plan_tiles(int64_t m, int64_t n, int64_t k, int sms, int64_t scratch_bytes) {
+  // microseconds per 64-deep k-step of one tile on one SM
+  static const struct { int bm, bn; double step_us; } kCand[4] = {
+      {256, 256, 0.74}, {256, 128, 0.52}, {128, 256, 0.58}, {128, 128, 0.42}};
+  static int force_ks = -1;
+  if (force_ks < 0) {
+    const char* e = getenv("B200Q_TC_KSPLIT");  // tuning aid: fixed split, 1 = never split
+    force_ks = e ? atoi(e) : 0;
+  }
+  const int kb_total = (int)(k / kBK);
+  TcPlan best = {128, 128, 1, 0};
+  double best_cost = 1e300;
   for (const auto& c : kCand) {
     if (c.bm == 256 && m <= 128) continue;
     if (c.bn == 256 && n <= 128) continue;
     const int64_t tiles = ((m + c.bm - 1) / c.bm) * ((n + c.bn - 1) / c.bn);
-    const double waves = (double)((tiles + sms - 1) / sms);
-    const double cost = waves * c.bm * c.bn / c.eff;
-    if (cost < best) { best = cost; *bm_out = c.bm; *bn_out = c.bn; }
+    for (int ks = 1; ks <= 8; ++ks) {
+      if (force_ks > 0 && ks != force_ks && !(ks == 1 && force_ks > kb_total / 2)) continue;
+      const int64_t bytes = ks > 1 ? tiles * ks * c.bm * c.bn * 4 : 0;
+      if (ks > 1 && (kb_total / ks < 2 || bytes > scratch_bytes)) break;
+      const double waves = (double)((tiles * ks + sms - 1) / sms);
+      double cost = waves * ((double)kb_total / ks + 6.0 + (ks > 1 ? 2.0 : 0.0)) * c.step_us;
+      if (ks > 1) cost += 2.5 + (double)ks * m * n * 4 / 3.0e6;  // reduce kernel: launch + 3 TB/s
+      if (cost < best_cost) {
+        best_cost = cost;
+        best = {c.bm, c.bn, ks, bytes};
+      }
+    }
   }
+  return best;
 }
 
 }  // namespace tc
@@ -654,12 +771,10 @@ bool tc_gemm_supported(int64_t size_m, int64_t size_n, int64_t size_k, int gm) {
   static int min_m = 0;
   if (min_m == 0) {
     const char* e = getenv("B200Q_TC_MIN_M");  // tuning aid: smallest M taken by this kernel
-    min_m = e ? atoi(e) : 65;
-    if (min_m < 1) min_m = 65;
+    min_m = e ? atoi(e) : 33;
+    if (min_m < 1) min_m = 33;
   }
-  // 33..64 rows: only where there are enough 128-column tiles to fill the GPU (measured: the
-  // 64-row decode kernel wins on narrower layers)
-  const bool rows_ok = size_m >= min_m || (size_m > 32 && size_n >= 16384);
+  const bool rows_ok = size_m >= min_m;
   return rows_ok && size_k % tc::kBK == 0 && size_n % 64 == 0 && gm != kLookup &&
          tc::get_encode_fn() != nullptr;  // group_blocks >= 2 is checked by the caller
 }
@@ -668,7 +783,7 @@ bool tc_gemm_supported(int64_t size_m, int64_t size_n, int64_t size_k, int gm) {
 int launch_tc_gemm(const void* a, int64_t lda, const uint32_t* b, const void* scales,
                    const uint32_t* zeros, const void* bias, void* c, int a_dtype, int bits,
                    int64_t size_m, int64_t size_n, int64_t size_k, int group_blocks,
-                   int channelwise, cudaStream_t stream) {
+                   int channelwise, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
   CUtensorMap map;
   const cuuint64_t gdim[2] = {(cuuint64_t)size_k, (cuuint64_t)size_m};
   const cuuint64_t gstride[1] = {(cuuint64_t)lda * 2};
@@ -684,22 +799,31 @@ int launch_tc_gemm(const void* a, int64_t lda, const uint32_t* b, const void* sc
   p.b = b; p.scales = scales; p.zeros = zeros; p.bias = bias; p.c = c;
   p.m = (int)size_m; p.n = (int)size_n; p.k = (int)size_k;
   p.group_blocks = group_blocks; p.channelwise = channelwise;
-  int bm = 128, bn = 128;
-  tc::choose_tile(size_m, size_n, bits, device_sm_count(), &bm, &bn);
-  if (const char* e = getenv("B200Q_TC_TILE")) {  // tuning aid: "BMxBN", e.g. 256x256
+  const tc::TcPlan plan = tc::plan_tiles(size_m, size_n, size_k, device_sm_count(), scratch_bytes);
+  int bm = plan.bm, bn = plan.bn;
+  p.ksplit = plan.ksplit;
+  if (const char* e = getenv("B200Q_TC_TILE")) {  // tuning aid: "BMxBN", e.g. 256x256 (no split)
     int fm = 0, fn = 0;
     if (sscanf(e, "%dx%d", &fm, &fn) == 2 && (fm == 128 || fm == 256) && (fn == 128 || fn == 256) &&
         (fm == 128 || size_m > 128)) {
       bm = fm;
       bn = fn;
+      p.ksplit = 1;
     }
   }
+  p.partials = static_cast<float*>(scratch);
   const bool has_zp = zeros != nullptr;
   if (a_dtype == B200Q_F16)
     return bits == 4 ? tc::launch_bits<half, 4>(map, p, has_zp, bm, bn, stream)
                      : tc::launch_bits<half, 8>(map, p, has_zp, bm, bn, stream);
   return bits == 4 ? tc::launch_bits<__nv_bfloat16, 4>(map, p, has_zp, bm, bn, stream)
                    : tc::launch_bits<__nv_bfloat16, 8>(map, p, has_zp, bm, bn, stream);
+}
+
+// Scratch the tensor-core kernel would like for this problem (fp32 partials of a k-split).
+int64_t tc_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k) {
+  if (size_m <= 32 || size_k % tc::kBK != 0 || size_n % 64 != 0) return 0;
+  return tc::plan_tiles(size_m, size_n, size_k, device_sm_count(), tc::kMaxSplitBytes).partial_bytes;
 }
 
 int tc_error_flag(bool reset) {

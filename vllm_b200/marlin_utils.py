@@ -88,10 +88,10 @@ def check_marlin_supported(quant_type: ScalarType, group_size: int, has_zp: bool
 def marlin_make_workspace_new(device: torch.device, max_blocks_per_sm: int = 2) -> torch.Tensor:
     """Zero-initialised int32 counters, one per CTA the GEMM may launch.  The
     GEMM accepts any length >= #SMs (what the reference allocates,
-    marlin_utils.py:237-245) and sizes its grid to fit; two per SM lets the
-    decode kernel keep two CTAs resident per SM."""
+    marlin_utils.py:237-245) and sizes its work to fit; the extra length lets the
+    tensor-core kernel split K on problems with few output tiles (four counters per tile)."""
     sms = torch.cuda.get_device_properties(device).multi_processor_count
-    return torch.zeros(sms * max_blocks_per_sm, dtype=torch.int, device=device,
+    return torch.zeros(max(sms * max_blocks_per_sm, 1024), dtype=torch.int, device=device,
                        requires_grad=False)
 
 
