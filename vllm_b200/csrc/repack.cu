@@ -190,8 +190,11 @@ permute_cols_small_kernel(const uint16_t* __restrict__ a, int64_t lda,
   const int k0 = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (k0 >= size_k) return;
   const uint16_t* src = a + (size_t)m * lda;
+  // the permutation is a constant of the layer: fetch it while the kernel before this one
+  // in the stream drains, then wait for that kernel (it produced `a` and may still read `out`)
   const int4 p0 = *reinterpret_cast<const int4*>(perm + k0);
   const int4 p1 = *reinterpret_cast<const int4*>(perm + k0 + 4);
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
   uint4 v;
   v.x = (uint32_t)src[p0.x] | ((uint32_t)src[p0.y] << 16);
   v.y = (uint32_t)src[p0.z] | ((uint32_t)src[p0.w] << 16);
@@ -208,10 +211,18 @@ int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* o
   if (size_m <= 64 && size_k % 8 == 0 && (reinterpret_cast<uintptr_t>(perm) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
     dim3 grid((unsigned)((size_k / 8 + 255) / 256), (unsigned)size_m);
-    permute_cols_small_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(a), lda, perm,
-                                                        static_cast<uint16_t*>(out), (int)size_k);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, permute_cols_small_kernel, static_cast<const uint16_t*>(a),
+                                     lda, perm, static_cast<uint16_t*>(out), (int)size_k));
     note_launch();
-    B200Q_CUDA_OK(cudaGetLastError());
     return B200Q_OK;
   }
   const size_t row_bytes = (size_t)size_k * 2;
