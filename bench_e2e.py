@@ -43,6 +43,8 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
         D.initialize_model_parallel(world)
+        if os.environ.get("E2E_NCCL_ONLY", "0") != "1":
+            D.enable_custom_all_reduce(dev)   # row-parallel outputs up to 512 KiB: peer-memory all-reduce
     cfg = LlamaConfig(num_layers=args.layers)
     model = LlamaDecoder(cfg, max_seq=args.prompt + args.new + 1, batch=args.batch, device=dev,
                          tp_rank=rank, tp_size=world)

@@ -160,6 +160,9 @@ __global__ void __launch_bounds__(256)
 permute_cols_kernel(const uint16_t* __restrict__ a, int64_t lda, const int32_t* __restrict__ perm,
                     uint16_t* __restrict__ out, int size_m, int size_k, int stage_in_smem) {
   extern __shared__ __align__(16) uint16_t row_buf[];
+  // 16-byte stores and permutation loads need K % 8 == 0 and aligned bases
+  const bool vec_out = (size_k % 8 == 0) && ((reinterpret_cast<uintptr_t>(perm) & 15) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
   // the GEMM that follows may start prefetching its weights right away
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   for (int m = blockIdx.x; m < size_m; m += gridDim.x) {
@@ -172,7 +175,21 @@ permute_cols_kernel(const uint16_t* __restrict__ a, int64_t lda, const int32_t* 
         reinterpret_cast<uint4*>(row_buf)[i] = reinterpret_cast<const uint4*>(src)[i];
       for (int i = vecs * 8 + threadIdx.x; i < size_k; i += blockDim.x) row_buf[i] = src[i];
       __syncthreads();
-      for (int k = threadIdx.x; k < size_k; k += blockDim.x) dst[k] = row_buf[perm[k]];
+      if (vec_out) {
+        // eight outputs per thread: two 16-byte loads of the permutation, one 16-byte store
+        for (int i = threadIdx.x; i < vecs; i += blockDim.x) {
+          const int4 p0 = __ldg(reinterpret_cast<const int4*>(perm) + 2 * i);
+          const int4 p1 = __ldg(reinterpret_cast<const int4*>(perm) + 2 * i + 1);
+          uint4 v;
+          v.x = (uint32_t)row_buf[p0.x] | ((uint32_t)row_buf[p0.y] << 16);
+          v.y = (uint32_t)row_buf[p0.z] | ((uint32_t)row_buf[p0.w] << 16);
+          v.z = (uint32_t)row_buf[p1.x] | ((uint32_t)row_buf[p1.y] << 16);
+          v.w = (uint32_t)row_buf[p1.z] | ((uint32_t)row_buf[p1.w] << 16);
+          reinterpret_cast<uint4*>(dst)[i] = v;
+        }
+      } else {
+        for (int k = threadIdx.x; k < size_k; k += blockDim.x) dst[k] = row_buf[perm[k]];
+      }
       __syncthreads();
     } else {
       for (int k = threadIdx.x; k < size_k; k += blockDim.x) dst[k] = src[perm[k]];
