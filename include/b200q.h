@@ -187,6 +187,42 @@ int b200q_marlin_gemm_all_reduce(
     int world, int64_t max_message_bytes, b200q_stream_t stream);
 
 /*
+ * residual += input; input = rms_norm(residual) * weight, in place, one row per token.
+ * With residual == NULL: input = rms_norm(input) * weight.
+ * Replaces: fused_add_rms_norm / rms_norm, csrc/layernorm_kernels.cu:17-58,60-149
+ *           (vllm/_custom_ops.py:328-339); same rounding points: the sum is rounded to
+ *           16 bits, the variance is taken from the rounded sum in fp32, (z * rstd) is
+ *           rounded, then multiplied by the weight in 16 bits.
+ *   input     [num_tokens, hidden_size] 16-bit, row stride ld_input elements
+ *   residual  [num_tokens, hidden_size] contiguous, or NULL
+ *   weight    [hidden_size]; hidden_size % 8 == 0; all pointers 16 B aligned
+ */
+int b200q_fused_add_rms_norm(void* input, int64_t ld_input, void* residual, const void* weight,
+                             float epsilon, int64_t num_tokens, int64_t hidden_size, int dtype,
+                             b200q_stream_t stream);
+
+/*
+ * The same with the SUM all-reduce of `input` over the peer link in front, in one
+ * kernel: what follows RowParallelLinear in a decoder layer (all-reduce, residual
+ * add, RMSNorm; the reference fuses these through a pattern-matching pass,
+ * vllm/compilation/collective_fusion.py:656-775).  `input` holds this rank's partial
+ * on entry (contiguous) and the normalised row on exit; link arguments as in
+ * b200q_all_reduce; num_tokens * hidden_size * 2 <= max_message_bytes.
+ */
+int b200q_all_reduce_fused_add_rms_norm(void* const* peer_bufs, uint32_t* state, int rank, int world,
+                                        int64_t max_message_bytes, void* input, void* residual,
+                                        const void* weight, float epsilon, int64_t num_tokens,
+                                        int64_t hidden_size, int dtype, b200q_stream_t stream);
+
+/*
+ * out[t, i] = silu(input[t, i]) * input[t, d + i]  (the MLP step between the gate_up and
+ * down projections).  Replaces: silu_and_mul, csrc/activation_kernels.cu:22-38,85-89.
+ *   input [num_tokens, 2 * d], out [num_tokens, d], contiguous, d % 8 == 0
+ */
+int b200q_silu_and_mul(void* out, const void* input, int64_t num_tokens, int64_t d, int dtype,
+                       b200q_stream_t stream);
+
+/*
  * b200q_marlin_gemm for callers that cannot allocate device memory (a plugin
  * running inside another framework's fixed memory plan, code that runs while a
  * stream is being captured, a process whose device memory belongs to another

@@ -103,6 +103,20 @@ def _worker(rank, world, port, q):
         g2.replay()
     torch.cuda.synchronize()
     ok &= bool(torch.equal(o1, want)) and bool(torch.equal(o2, want))
+    # all-reduce + residual add + RMSNorm in one kernel == the three steps one after another
+    from vllm_b200 import _custom_ops as ops
+    car = D._CUSTOM_AR
+    common = torch.Generator(device=dev).manual_seed(77)        # same residual / weight on every rank
+    for (m, n) in ((1, 4096), (48, 4096), (5, 1024), (64, 4096)):
+        part = torch.randn((m, n), device=dev, generator=gen).to(torch.bfloat16)
+        res = torch.randn((m, n), device=dev, generator=common).to(torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(n, device=dev, generator=common)).to(torch.bfloat16)
+        want_x, want_res = D.tensor_model_parallel_all_reduce(part), res.clone()
+        ops.fused_add_rms_norm(want_x, want_res, w, 1e-5)
+        got_x, got_res = part.clone(), res.clone()
+        ok &= car.all_reduce_add_rms_norm(got_x, got_res, w, 1e-5)
+        torch.cuda.synchronize()
+        ok &= bool(torch.equal(got_x, want_x)) and bool(torch.equal(got_res, want_res))
     ok &= lib.b200q_device_error(1) == 0
     q.put((rank, ok))
     dist.barrier()

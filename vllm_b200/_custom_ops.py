@@ -382,5 +382,50 @@ def gptq_marlin_gemm(a: torch.Tensor, c: torch.Tensor | None, b_q_weight: torch.
                                  use_atomic_add, use_fp32_reduce, is_zp_float)
 
 
+def _dtype_code(t: torch.Tensor) -> int:
+    _check(t.dtype in (torch.float16, torch.bfloat16), "only float16 and bfloat16 are supported")
+    return _lib.BF16 if t.dtype == torch.bfloat16 else _lib.F16
+
+
+def fused_add_rms_norm(input: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
+                       epsilon: float) -> None:
+    """In place: residual += input; input = rms_norm(residual) * weight
+    (vllm/_custom_ops.py:336-339)."""
+    _check(input.is_cuda and input.stride(-1) == 1, "input must be a CUDA tensor with unit inner stride")
+    _check(residual.is_contiguous() and weight.is_contiguous(), "residual / weight must be contiguous")
+    _check(residual.dtype == input.dtype == weight.dtype, "dtypes must match")
+    n = input.size(-1)
+    x2 = input.view(-1, n)
+    with _on_device(input.device):
+        rc = _L.b200q_fused_add_rms_norm(_ptr(x2), x2.stride(0), _ptr(residual), _ptr(weight),
+                                         float(epsilon), x2.size(0), n, _dtype_code(input),
+                                         _stream(input.device))
+    _lib.check(rc, "fused_add_rms_norm")
+
+
+def rms_norm(out: torch.Tensor, input: torch.Tensor, weight: torch.Tensor, epsilon: float) -> None:
+    """out = rms_norm(input) * weight (vllm/_custom_ops.py:328-333)."""
+    _check(out.is_contiguous() and out.shape == input.shape and out.dtype == input.dtype,
+           "out must be contiguous with the shape and dtype of input")
+    out.copy_(input)
+    n = out.size(-1)
+    with _on_device(out.device):
+        rc = _L.b200q_fused_add_rms_norm(_ptr(out), n, None, _ptr(weight), float(epsilon),
+                                         out.numel() // n, n, _dtype_code(out), _stream(out.device))
+    _lib.check(rc, "rms_norm")
+
+
+def silu_and_mul(out: torch.Tensor, input: torch.Tensor) -> None:
+    """out = silu(input[..., :d]) * input[..., d:] (vllm/_custom_ops.py, torch.ops._C.silu_and_mul)."""
+    d = input.size(-1) // 2
+    _check(input.is_cuda and input.is_contiguous() and out.is_contiguous(), "tensors must be contiguous")
+    _check(out.size(-1) == d and out.numel() * 2 == input.numel() and out.dtype == input.dtype,
+           "out must be [..., d] for input [..., 2 * d]")
+    with _on_device(input.device):
+        rc = _L.b200q_silu_and_mul(_ptr(out), _ptr(input), out.numel() // d, d, _dtype_code(input),
+                                   _stream(input.device))
+    _lib.check(rc, "silu_and_mul")
+
+
 def permute_cols(a: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
     return _ops.permute_cols(a, perm)

@@ -30,6 +30,9 @@ EXPORTS = (
     "b200q_all_reduce_buffer_bytes",
     "b200q_all_reduce",
     "b200q_marlin_gemm_all_reduce",
+    "b200q_fused_add_rms_norm",
+    "b200q_all_reduce_fused_add_rms_norm",
+    "b200q_silu_and_mul",
 )
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4
@@ -90,6 +93,13 @@ def load() -> ctypes.CDLL:
         vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i64, i64, i64, i64, u32, vp]
     lib.b200q_all_reduce_state_bytes.restype = c.c_size_t
     lib.b200q_all_reduce.restype = i32
+    lib.b200q_fused_add_rms_norm.restype = i32
+    lib.b200q_fused_add_rms_norm.argtypes = [vp, i64, vp, vp, c.c_float, i64, i64, i32, vp]
+    lib.b200q_all_reduce_fused_add_rms_norm.restype = i32
+    lib.b200q_all_reduce_fused_add_rms_norm.argtypes = [vp, vp, i32, i32, i64, vp, vp, vp, c.c_float,
+                                                        i64, i64, i32, vp]
+    lib.b200q_silu_and_mul.restype = i32
+    lib.b200q_silu_and_mul.argtypes = [vp, vp, i64, i64, i32, vp]
     lib.b200q_all_reduce_buffer_bytes.restype = c.c_size_t
     lib.b200q_all_reduce_buffer_bytes.argtypes = [i32, i64]
     lib.b200q_all_reduce.argtypes = [vp, vp, i32, i32, i64, vp, vp, i64, i32, vp]

@@ -32,7 +32,7 @@ def _units():
         for bits in (4, 8):
             units.append(("gemm_stream_inst.cu", f"gemm_stream_{'bf16' if bf16 else 'f16'}_w{bits}.o",
                           [f"-DINST_BF16={bf16}", f"-DINST_BITS={bits}"]))
-    for extra in ("gemm_tc.cu", "noalloc.cu", "allreduce.cu"):
+    for extra in ("gemm_tc.cu", "noalloc.cu", "allreduce.cu", "elementwise.cu"):
         if os.path.exists(os.path.join(CSRC, extra)):
             units.append((extra, extra.replace(".cu", ".o"), []))
     return units

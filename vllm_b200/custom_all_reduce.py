@@ -99,3 +99,22 @@ class CustomAllreduce:
             vp(torch.cuda.current_stream(self.device).cuda_stream))
         _lib.check(rc, "b200q_all_reduce")
         return out
+
+    def all_reduce_add_rms_norm(self, inp: torch.Tensor, residual: torch.Tensor | None,
+                                weight: torch.Tensor, epsilon: float) -> bool:
+        """In place and in one kernel: inp = all_reduce(inp); residual += inp;
+        inp = rms_norm(residual) * weight (residual None: plain rms_norm of the sum).
+        Returns False (nothing done) when the input does not qualify."""
+        if not self.should_custom_ar(inp) or inp.size(-1) % 8 != 0:
+            return False
+        n = inp.size(-1)
+        vp = ctypes.c_void_p
+        rc = self.lib.b200q_all_reduce_fused_add_rms_norm(
+            vp(self.data_hdl.buffer_ptrs_dev), vp(self.state.data_ptr()), self.rank,
+            self.world_size, self.max_size, vp(inp.data_ptr()),
+            vp(residual.data_ptr()) if residual is not None else None, vp(weight.data_ptr()),
+            float(epsilon), inp.numel() // n, n,
+            _lib.BF16 if inp.dtype == torch.bfloat16 else _lib.F16,
+            vp(torch.cuda.current_stream(self.device).cuda_stream))
+        _lib.check(rc, "b200q_all_reduce_fused_add_rms_norm")
+        return True

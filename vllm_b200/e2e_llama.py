@@ -4,8 +4,11 @@ measurement (random-init Llama-3-8B shape, GPTQ uint4b8 g128).
 
 Only what the measurement needs is here: RMSNorm, RoPE, grouped-query attention
 over a static KV cache (torch SDPA), SiLU-gated MLP, greedy sampling; the layer
-order and the four projections per block follow the reference's model
-(vllm/model_executor/models/llama.py:73-347).  Embedding and lm_head stay 16-bit
+order, the four projections per block and the (hidden, residual) hand-over between
+blocks follow the reference's model (vllm/model_executor/models/llama.py:73-347).
+The residual add + RMSNorm and SiLU * mul steps next to the projections run through
+this package's kernels; after a row-parallel projection the all-reduce is either
+inside the GEMM kernel (up to 32 rows) or inside the add + RMSNorm kernel.  Embedding and lm_head stay 16-bit
 and replicated (the reference quantizes lm_head only when the checkpoint says
 so, gptq_marlin.py:198).  Attention, norms and sampling use stock torch ops: they
 are outside the hot path this package replaces.
@@ -17,6 +20,8 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
+from . import _custom_ops as ops
+from . import distributed as D
 from .linear import MergedColumnParallelLinear, QKVParallelLinear, RowParallelLinear
 from .quantization import GPTQMarlinConfig
 
@@ -68,14 +73,31 @@ class DecoderLayer(torch.nn.Module):
         self.n_q = self.qkv_proj.num_heads
         self.n_kv = self.qkv_proj.num_kv_heads
 
-    def forward(self, x, cos, sin, k_cache, v_cache, pos_index, attn_mask, prefill_len):
-        """x: [B, T, H].  prefill (prefill_len = T > 0): causal attention inside the prompt, KV
-        written to [0, T).  decode (T == 1): KV written at pos_index, attention over the cache
-        under attn_mask [1, 1, 1, S]."""
+    def _row_parallel_then_norm(self, proj, inp, residual, weight):
+        """proj(inp) summed over the tensor-parallel ranks, added to the residual, normalised.
+        Returns the normalised activations [rows, hidden]; the residual is updated in place."""
+        eps = self.cfg.rms_eps
+        rows = inp.shape[0]
+        car = D._CUSTOM_AR
+        if proj.tp_size > 1 and car is not None and rows > 32:
+            part = proj(inp, reduce=False)
+            if car.all_reduce_add_rms_norm(part, residual, weight, eps):
+                return part
+            out = D.tensor_model_parallel_all_reduce(part)
+        else:
+            out = proj(inp)          # all-reduce inside the GEMM kernel (or NCCL without a link)
+        ops.fused_add_rms_norm(out, residual, weight, eps)
+        return out
+
+    def forward(self, x, residual, cos, sin, k_cache, v_cache, pos_index, attn_mask, prefill_len,
+                next_norm):
+        """x: [B, T, H], normalised input of the block; residual: [B * T, H], updated in place.
+        prefill (prefill_len = T > 0): causal attention inside the prompt, KV written to [0, T).
+        decode (T == 1): KV written at pos_index, attention over the cache under attn_mask
+        [1, 1, 1, S].  Returns the input of the next block, normalised with `next_norm`."""
         cfg = self.cfg
         B, T, _ = x.shape
-        h = rms_norm(x, self.input_norm, cfg.rms_eps)
-        qkv = self.qkv_proj(h.view(B * T, -1)).view(B, T, -1)
+        qkv = self.qkv_proj(x.view(B * T, -1)).view(B, T, -1)
         q, k, v = qkv.split([self.n_q * cfg.head_dim, self.n_kv * cfg.head_dim,
                              self.n_kv * cfg.head_dim], dim=-1)
         q = q.view(B, T, self.n_q, cfg.head_dim).transpose(1, 2)
@@ -92,12 +114,12 @@ class DecoderLayer(torch.nn.Module):
             attn = F.scaled_dot_product_attention(q, k_cache, v_cache, attn_mask=attn_mask,
                                                   enable_gqa=True)
         attn = attn.transpose(1, 2).reshape(B * T, -1)
-        x = x + self.o_proj(attn).view(B, T, -1)
-        h = rms_norm(x, self.post_norm, cfg.rms_eps)
-        gu = self.gate_up_proj(h.view(B * T, -1))
-        gate, up = gu.chunk(2, dim=-1)
-        x = x + self.down_proj(F.silu(gate) * up).view(B, T, -1)
-        return x
+        h = self._row_parallel_then_norm(self.o_proj, attn, residual, self.post_norm)
+        gu = self.gate_up_proj(h)
+        act = torch.empty((B * T, gu.shape[-1] // 2), dtype=gu.dtype, device=gu.device)
+        ops.silu_and_mul(act, gu)
+        h = self._row_parallel_then_norm(self.down_proj, act, residual, next_norm)
+        return h.view(B, T, -1)
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -136,23 +158,31 @@ class LlamaDecoder(torch.nn.Module):
     def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens [B, T] -> next token ids [B]."""
         B, T = tokens.shape
-        x = self.embed[tokens]
+        x = self._run_layers(self.embed[tokens], self.cos[:T], self.sin[:T], None, None, T)
+        return (x[:, -1] @ self.lm_head.t()).argmax(-1)
+
+    def _run_layers(self, emb, cos, sin, pos_index, attn_mask, prefill_len):
+        """emb [B, T, H] -> final-norm output [B, T, H]."""
+        B, T, H = emb.shape
+        residual = emb.reshape(B * T, H).clone()
+        x = torch.empty_like(residual)
+        ops.rms_norm(x, residual, self.layers[0].input_norm, self.cfg.rms_eps)
+        x = x.view(B, T, H)
+        n = len(self.layers)
         for i, layer in enumerate(self.layers):
-            x = layer(x, self.cos[:T], self.sin[:T], self.k_cache[i], self.v_cache[i], None, None, T)
-        x = rms_norm(x[:, -1], self.final_norm, self.cfg.rms_eps)
-        return (x @ self.lm_head.t()).argmax(-1)
+            next_norm = self.layers[i + 1].input_norm if i + 1 < n else self.final_norm
+            x = layer(x, residual, cos, sin, self.k_cache[i], self.v_cache[i], pos_index, attn_mask,
+                      prefill_len, next_norm)
+        return x
 
     @torch.no_grad()
     def decode_step(self, tokens: torch.Tensor, pos_index: torch.Tensor,
                     attn_mask: torch.Tensor) -> torch.Tensor:
         """One token per sequence.  tokens [B]; pos_index int64 [1] (cache slot to write);
         attn_mask bool [1, 1, 1, max_seq] with the valid cache slots set."""
-        x = self.embed[tokens][:, None]
         cos, sin = self.cos.index_select(0, pos_index), self.sin.index_select(0, pos_index)
-        for i, layer in enumerate(self.layers):
-            x = layer(x, cos, sin, self.k_cache[i], self.v_cache[i], pos_index, attn_mask, 0)
-        x = rms_norm(x[:, 0], self.final_norm, self.cfg.rms_eps)
-        return (x @ self.lm_head.t()).argmax(-1)
+        x = self._run_layers(self.embed[tokens][:, None], cos, sin, pos_index, attn_mask, 0)
+        return (x[:, 0] @ self.lm_head.t()).argmax(-1)
 
 
 @torch.no_grad()

@@ -163,11 +163,14 @@ class RowParallelLinear(LinearBase):
                       loaded_shard_id=None) -> None:
         param.load_row_parallel_weight(loaded_weight, self.tp_rank, self.tp_size)
 
-    def forward(self, input_: torch.Tensor, all_reduce=tensor_model_parallel_all_reduce) -> torch.Tensor:
+    def forward(self, input_: torch.Tensor, all_reduce=tensor_model_parallel_all_reduce,
+                reduce: bool = True) -> torch.Tensor:
+        """reduce=False returns this rank's partial sum (for a caller that fuses the all-reduce
+        with what follows, e.g. residual add + RMSNorm)."""
         if not self.input_is_parallel and self.tp_size > 1:
             input_ = input_.chunk(self.tp_size, dim=-1)[self.tp_rank].contiguous()
         bias = self.bias if (self.tp_rank == 0 or self.tp_size == 1) else None
-        if not (self.reduce_results and self.tp_size > 1):
+        if not (reduce and self.reduce_results and self.tp_size > 1):
             return self.quant_method.apply(self, input_, bias)
         if all_reduce is not tensor_model_parallel_all_reduce:
             return all_reduce(self.quant_method.apply(self, input_, bias))
