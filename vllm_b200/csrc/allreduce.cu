@@ -49,33 +49,28 @@ __global__ void __launch_bounds__(kThreads, 1) allreduce_oneshot_kernel(const Ar
     }
   }
   for (long long v = v0; v < p.n_vec; v += stride) {
+    uint32_t d[kArMaxWorld][4];
+    if (!ar_collect<4>(l, mybuf, (size_t)v * 32, flag, d)) break;
+    const uint4 x = in[v];
     float acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-    bool ok = true;
-    for (int r = 0; r < l.world; ++r) {
-      uint32_t w0, w1, w2, w3;
-      if (r == l.rank) {
-        const uint4 x = in[v];
-        w0 = x.x; w1 = x.y; w2 = x.z; w3 = x.w;
-      } else {
-        const char* src = mybuf + r * l.slot_bytes + v * 32;
-        if (!ar_get2(src, flag, w0, w1) || !ar_get2(src + 16, flag, w2, w3)) {
-          atomicCAS(l.error, 0, 0x100 | r);
-          ok = false;
-          break;
-        }
+#pragma unroll
+    for (int r = 0; r < kArMaxWorld; ++r) {
+      if (r < l.world) {
+        const bool me = r == l.rank;
+        const uint32_t w0 = me ? x.x : d[r][0], w1 = me ? x.y : d[r][1];
+        const uint32_t w2 = me ? x.z : d[r][2], w3 = me ? x.w : d[r][3];
+        acc[0] += Pair<T>::to_float((uint16_t)(w0 & 0xffffu));
+        acc[1] += Pair<T>::to_float((uint16_t)(w0 >> 16));
+        acc[2] += Pair<T>::to_float((uint16_t)(w1 & 0xffffu));
+        acc[3] += Pair<T>::to_float((uint16_t)(w1 >> 16));
+        acc[4] += Pair<T>::to_float((uint16_t)(w2 & 0xffffu));
+        acc[5] += Pair<T>::to_float((uint16_t)(w2 >> 16));
+        acc[6] += Pair<T>::to_float((uint16_t)(w3 & 0xffffu));
+        acc[7] += Pair<T>::to_float((uint16_t)(w3 >> 16));
       }
-      acc[0] += Pair<T>::to_float((uint16_t)(w0 & 0xffffu));
-      acc[1] += Pair<T>::to_float((uint16_t)(w0 >> 16));
-      acc[2] += Pair<T>::to_float((uint16_t)(w1 & 0xffffu));
-      acc[3] += Pair<T>::to_float((uint16_t)(w1 >> 16));
-      acc[4] += Pair<T>::to_float((uint16_t)(w2 & 0xffffu));
-      acc[5] += Pair<T>::to_float((uint16_t)(w2 >> 16));
-      acc[6] += Pair<T>::to_float((uint16_t)(w3 & 0xffffu));
-      acc[7] += Pair<T>::to_float((uint16_t)(w3 >> 16));
     }
-    if (!ok) break;
     uint4 o;
     o.x = (uint32_t)Pair<T>::from_float(acc[0]) | ((uint32_t)Pair<T>::from_float(acc[1]) << 16);
     o.y = (uint32_t)Pair<T>::from_float(acc[2]) | ((uint32_t)Pair<T>::from_float(acc[3]) << 16);

@@ -32,7 +32,7 @@ constexpr uint32_t kArSpinLimit = 1u << 21;  // polls of local memory: a second 
 struct ArLink {
   void* const* bufs;         // device array [world]: every rank's receive buffer
   uint32_t* state;           // local: {call number, arrivals}
-  int* error;                // local: 0 = ok, else 0x100 | peer rank of the first poll that timed out
+  int* error;                // local: 0 = ok, 0x1ff after a poll of the peers' packets timed out
   long long slot_bytes;      // packet bytes of one (parity, rank) slot = 2 x the largest message
   int rank, world;           // world == 0: link not in use
 };
@@ -56,24 +56,43 @@ __device__ __forceinline__ void ar_put2(void* dst, uint32_t d0, uint32_t d1, uin
                "r"(d1)
                : "memory");
 }
-__device__ __forceinline__ bool ar_get1(const void* src, uint32_t flag, uint32_t& d) {
+// Collect P adjacent packets (P = 1, 2 or 4) at byte offset `off` of every peer's slot
+// in this rank's buffer.  The loads of all peers are issued together and polled as a
+// batch, so the wait costs about one memory latency, not one per peer.  d[r] is left
+// untouched for r == rank and r >= world.  Returns false on time-out.
+template <int P>
+__device__ __forceinline__ bool ar_collect(const ArLink& l, const char* mybuf, size_t off,
+                                           uint32_t flag, uint32_t (&d)[kArMaxWorld][P]) {
+  static_assert(P == 1 || P == 2 || P == 4, "packets per element");
   for (uint32_t spin = 0; spin < kArSpinLimit; ++spin) {
-    uint32_t f;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];\n" : "=r"(d), "=r"(f) : "l"(src)
-                 : "memory");
-    if (f == flag) return true;
+    bool all = true;
+#pragma unroll
+    for (int r = 0; r < kArMaxWorld; ++r) {
+      if (r < l.world && r != l.rank) {
+        const char* src = mybuf + r * l.slot_bytes + off;
+        if constexpr (P == 1) {
+          uint32_t f;
+          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];\n"
+                       : "=r"(d[r][0]), "=r"(f)
+                       : "l"(src)
+                       : "memory");
+          all = all && f == flag;
+        } else {
+#pragma unroll
+          for (int h = 0; h < P / 2; ++h) {
+            uint32_t f0, f1;
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                         : "=r"(d[r][2 * h]), "=r"(f0), "=r"(d[r][2 * h + 1]), "=r"(f1)
+                         : "l"(src + 16 * h)
+                         : "memory");
+            all = all && f0 == flag && f1 == flag;
+          }
+        }
+      }
+    }
+    if (all) return true;
   }
-  return false;
-}
-__device__ __forceinline__ bool ar_get2(const void* src, uint32_t flag, uint32_t& d0, uint32_t& d1) {
-  for (uint32_t spin = 0; spin < kArSpinLimit; ++spin) {
-    uint32_t f0, f1;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];\n"
-                 : "=r"(d0), "=r"(f0), "=r"(d1), "=r"(f1)
-                 : "l"(src)
-                 : "memory");
-    if (f0 == flag && f1 == flag) return true;
-  }
+  atomicCAS(l.error, 0, 0x1ff);
   return false;
 }
 

@@ -81,24 +81,24 @@ __global__ void __launch_bounds__(kNormThreads, 1) fused_add_rms_norm_kernel(con
     uint4 x = xrow[v];
     if (l.world) {
       // all-reduce: fp32 sum in rank order, one rounding (what the separate kernel stores)
+      uint32_t d[kArMaxWorld][4];
+      if (!ar_collect<4>(l, mybuf, ((size_t)row * vecs + v) * 32, flag, d)) {
+        ok = false;
+        break;
+      }
       float acc[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      const size_t pkt = ((size_t)row * vecs + v) * 32;
-      for (int r = 0; r < l.world; ++r) {
-        uint32_t w0 = x.x, w1 = x.y, w2 = x.z, w3 = x.w;
-        if (r != l.rank) {
-          const char* src = mybuf + r * l.slot_bytes + pkt;
-          if (!ar_get2(src, flag, w0, w1) || !ar_get2(src + 16, flag, w2, w3)) {
-            atomicCAS(l.error, 0, 0x100 | r);
-            ok = false;
-            break;
-          }
+#pragma unroll
+      for (int r = 0; r < kArMaxWorld; ++r) {
+        if (r < l.world) {
+          const bool me = r == l.rank;
+          const uint32_t w0 = me ? x.x : d[r][0], w1 = me ? x.y : d[r][1];
+          const uint32_t w2 = me ? x.z : d[r][2], w3 = me ? x.w : d[r][3];
+          acc[0] += lo_f<T>(w0); acc[1] += hi_f<T>(w0); acc[2] += lo_f<T>(w1); acc[3] += hi_f<T>(w1);
+          acc[4] += lo_f<T>(w2); acc[5] += hi_f<T>(w2); acc[6] += lo_f<T>(w3); acc[7] += hi_f<T>(w3);
         }
-        acc[0] += lo_f<T>(w0); acc[1] += hi_f<T>(w0); acc[2] += lo_f<T>(w1); acc[3] += hi_f<T>(w1);
-        acc[4] += lo_f<T>(w2); acc[5] += hi_f<T>(w2); acc[6] += lo_f<T>(w3); acc[7] += hi_f<T>(w3);
       }
-      if (!ok) break;
       x.x = pack2<T>(acc[0], acc[1]); x.y = pack2<T>(acc[2], acc[3]);
       x.z = pack2<T>(acc[4], acc[5]); x.w = pack2<T>(acc[6], acc[7]);
     }

@@ -689,27 +689,22 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
       for (int i = 0; i < MT; ++i) {
         if (!blk_mine(i)) continue;
         const size_t el = (size_t)(i * 8 + o_row) * p.n + n_base;
+        uint32_t d[kArMaxWorld][Cfg::kEpt / 2];
+        if (!ar_collect<Cfg::kEpt / 2>(l, mybuf, el * 4, flag, d)) break;
         float sum[Cfg::kEpt];
 #pragma unroll
         for (int e = 0; e < Cfg::kEpt; ++e) sum[e] = 0.f;
-        bool ok = true;
-        for (int r = 0; r < l.world; ++r) {
-          uint32_t v[2] = {packed[i][0], Cfg::kEpt == 4 ? packed[i][Cfg::kEpt / 2 - 1] : 0u};
-          if (r != l.rank) {
-            const char* src = mybuf + r * l.slot_bytes + el * 4;
-            ok = (Cfg::kEpt == 4) ? ar_get2(src, flag, v[0], v[1]) : ar_get1(src, flag, v[0]);
-            if (!ok) {
-              atomicCAS(l.error, 0, 0x100 | r);
-              break;
+#pragma unroll
+        for (int r = 0; r < kArMaxWorld; ++r) {
+          if (r < l.world) {
+#pragma unroll
+            for (int e = 0; e < Cfg::kEpt / 2; ++e) {
+              const uint32_t v = (r == l.rank) ? packed[i][e] : d[r][e];
+              sum[2 * e] += Pair<T>::to_float((uint16_t)(v & 0xffffu));
+              sum[2 * e + 1] += Pair<T>::to_float((uint16_t)(v >> 16));
             }
           }
-#pragma unroll
-          for (int e = 0; e < Cfg::kEpt / 2; ++e) {
-            sum[2 * e] += Pair<T>::to_float((uint16_t)(v[e] & 0xffffu));
-            sum[2 * e + 1] += Pair<T>::to_float((uint16_t)(v[e] >> 16));
-          }
         }
-        if (!ok) break;
         uint32_t o[2];
 #pragma unroll
         for (int e = 0; e < Cfg::kEpt / 2; ++e)
