@@ -298,11 +298,16 @@ def run_ours(args, world, rank, local_rank):
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in shapes]
     t_all0, t_all1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    align = torch.zeros(1, device=dev) if dist is not None else None
     if not use_graphs:
         before = lib.b200q_kernel_launches()
     with torch.cuda.stream(stream):
         t_all0.record()
         for (e0, e1), (fn, _) in zip(ev, timed):
+            if align is not None:
+                # ranks drift apart over the shapes without a collective; without this the whole
+                # drift would be booked on the first row-parallel shape that follows
+                dist.all_reduce(align)
             e0.record()
             fn()
             e1.record()

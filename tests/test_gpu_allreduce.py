@@ -124,12 +124,17 @@ def _worker(rank, world, port, q):
     os._exit(0)
 
 
-def test_custom_all_reduce_matches_nccl():
+@pytest.mark.parametrize("twoshot", [False, True])
+def test_custom_all_reduce_matches_nccl(twoshot, monkeypatch):
+    """twoshot: the owner-reduces variant, forced on for every size and for two ranks."""
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least two GPUs")
-    world = 2
+    if twoshot:                      # read by the library in the child processes
+        monkeypatch.setenv("B200Q_AR_TWOSHOT_MIN", "0")
+        monkeypatch.setenv("B200Q_AR_TWOSHOT_WORLD", "2")
+    world = min(4, torch.cuda.device_count()) if twoshot else 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()

@@ -5,6 +5,8 @@
 // The counterpart in the reference is the custom all-reduce of
 // csrc/custom_all_reduce.cuh:298-314 (one-stage variant, pull-based, two barriers,
 // unbounded waits).
+#include <cstdlib>
+
 #include "ar_link.cuh"
 #include "common.cuh"
 
@@ -82,6 +84,89 @@ __global__ void __launch_bounds__(kThreads, 1) allreduce_oneshot_kernel(const Ar
   if (threadIdx.x == 0) ar_arrive(l, call, gridDim.x);
 }
 
+// Two-shot variant for larger messages on four or more ranks: every rank owns a chunk of
+// the message.  Phase 1 sends each vector only to the owner of its chunk, the owner sums
+// in rank order and sends the reduced vector to everybody (phase 2), and everybody picks
+// up the other owners' chunks (phase 3).  Per rank about twice the message crosses NVLink
+// instead of (world - 1) times.  Partial and reduced packets of one sender never share
+// an offset of its slot: the former sit in the receiver's chunk, the latter in the sender's.
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) allreduce_twoshot_kernel(const ArParams p) {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  const ArLink& l = p.link;
+  const uint32_t call = ar_ld_volatile(l.state);
+  const uint32_t flag = ar_flag(call);
+  const long long parity_off = (long long)(call & 1) * l.world * l.slot_bytes;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint4* in = static_cast<const uint4*>(p.in);
+  uint4* out = static_cast<uint4*>(p.out);
+  const char* mybuf = static_cast<const char*>(l.bufs[l.rank]) + parity_off;
+  const long long chunk = (p.n_vec + l.world - 1) / l.world;
+  const long long mine_off = parity_off + (long long)l.rank * l.slot_bytes;
+
+  for (long long v = v0; v < p.n_vec; v += stride) {
+    const int owner = (int)(v / chunk);
+    if (owner == l.rank) continue;
+    const uint4 x = in[v];
+    char* dst = static_cast<char*>(l.bufs[owner]) + mine_off + v * 32;
+    ar_put2(dst, x.x, x.y, flag);
+    ar_put2(dst + 16, x.z, x.w, flag);
+  }
+  const long long lo = (long long)l.rank * chunk;
+  const long long hi = lo + chunk < p.n_vec ? lo + chunk : p.n_vec;
+  bool ok = true;
+  for (long long v = lo + v0; v < hi && ok; v += stride) {
+    uint32_t d[kArMaxWorld][4];
+    if (!ar_collect<4>(l, mybuf, (size_t)v * 32, flag, d)) {
+      ok = false;
+      break;
+    }
+    const uint4 x = in[v];
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int r = 0; r < kArMaxWorld; ++r) {
+      if (r < l.world) {
+        const bool me = r == l.rank;
+        const uint32_t w0 = me ? x.x : d[r][0], w1 = me ? x.y : d[r][1];
+        const uint32_t w2 = me ? x.z : d[r][2], w3 = me ? x.w : d[r][3];
+        acc[0] += Pair<T>::to_float((uint16_t)(w0 & 0xffffu));
+        acc[1] += Pair<T>::to_float((uint16_t)(w0 >> 16));
+        acc[2] += Pair<T>::to_float((uint16_t)(w1 & 0xffffu));
+        acc[3] += Pair<T>::to_float((uint16_t)(w1 >> 16));
+        acc[4] += Pair<T>::to_float((uint16_t)(w2 & 0xffffu));
+        acc[5] += Pair<T>::to_float((uint16_t)(w2 >> 16));
+        acc[6] += Pair<T>::to_float((uint16_t)(w3 & 0xffffu));
+        acc[7] += Pair<T>::to_float((uint16_t)(w3 >> 16));
+      }
+    }
+    uint4 o;
+    o.x = (uint32_t)Pair<T>::from_float(acc[0]) | ((uint32_t)Pair<T>::from_float(acc[1]) << 16);
+    o.y = (uint32_t)Pair<T>::from_float(acc[2]) | ((uint32_t)Pair<T>::from_float(acc[3]) << 16);
+    o.z = (uint32_t)Pair<T>::from_float(acc[4]) | ((uint32_t)Pair<T>::from_float(acc[5]) << 16);
+    o.w = (uint32_t)Pair<T>::from_float(acc[6]) | ((uint32_t)Pair<T>::from_float(acc[7]) << 16);
+    out[v] = o;
+    for (int r = 0; r < l.world; ++r) {
+      if (r == l.rank) continue;
+      char* dst = static_cast<char*>(l.bufs[r]) + mine_off + v * 32;
+      ar_put2(dst, o.x, o.y, flag);
+      ar_put2(dst + 16, o.z, o.w, flag);
+    }
+  }
+  for (long long v = v0; v < p.n_vec && ok; v += stride) {
+    const int owner = (int)(v / chunk);
+    if (owner == l.rank) continue;
+    uint4 o;
+    if (!ar_get4(l, mybuf + (long long)owner * l.slot_bytes + v * 32, flag, o.x, o.y, o.z, o.w)) break;
+    out[v] = o;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) ar_arrive(l, call, gridDim.x);
+}
+
 }  // namespace ar
 
 int ar_error_flag(bool reset) {
@@ -131,10 +216,22 @@ int launch_all_reduce(const ArLink& link, const void* in, void* out, int64_t n_e
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  // two-shot from 256 KiB on four or more ranks (B200Q_AR_TWOSHOT_MIN overrides the size in bytes)
+  static const long long twoshot_min = [] {
+    const char* e = getenv("B200Q_AR_TWOSHOT_MIN");
+    return e ? atoll(e) : 256ll * 1024;
+  }();
+  static const int twoshot_world = [] {
+    const char* e = getenv("B200Q_AR_TWOSHOT_WORLD");  // smallest group that uses it (tests: 2)
+    return e ? atoi(e) : 4;
+  }();
+  const bool twoshot = link.world >= twoshot_world && n_elems * 2 >= twoshot_min;
   if (dtype == B200Q_F16)
-    B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, ar::allreduce_oneshot_kernel<half>, p));
+    B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, twoshot ? ar::allreduce_twoshot_kernel<half>
+                                                   : ar::allreduce_oneshot_kernel<half>, p));
   else
-    B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, ar::allreduce_oneshot_kernel<__nv_bfloat16>, p));
+    B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, twoshot ? ar::allreduce_twoshot_kernel<__nv_bfloat16>
+                                                   : ar::allreduce_oneshot_kernel<__nv_bfloat16>, p));
   note_launch();
   return B200Q_OK;
 }

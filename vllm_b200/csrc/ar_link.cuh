@@ -96,6 +96,25 @@ __device__ __forceinline__ bool ar_collect(const ArLink& l, const char* mybuf, s
   return false;
 }
 
+// Four adjacent packets (32 bytes) of one peer.
+__device__ __forceinline__ bool ar_get4(const ArLink& l, const char* src, uint32_t flag, uint32_t& w0,
+                                        uint32_t& w1, uint32_t& w2, uint32_t& w3) {
+  for (uint32_t spin = 0; spin < kArSpinLimit; ++spin) {
+    uint32_t f0, f1, f2, f3;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(w0), "=r"(f0), "=r"(w1), "=r"(f1)
+                 : "l"(src)
+                 : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(w2), "=r"(f2), "=r"(w3), "=r"(f3)
+                 : "l"(src + 16)
+                 : "memory");
+    if (f0 == flag && f1 == flag && f2 == flag && f3 == flag) return true;
+  }
+  atomicCAS(l.error, 0, 0x1ff);
+  return false;
+}
+
 // One thread per CTA, once, after all threads of the CTA have read the call number
 // and finished polling.
 __device__ __forceinline__ void ar_arrive(const ArLink& l, uint32_t call, uint32_t n_ctas) {
