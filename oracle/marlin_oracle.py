@@ -348,6 +348,21 @@ def dequantize(q: np.ndarray, scales: np.ndarray, dtype: str, *, bias: int = 0,
     return round_to_dtype(w_int * s, dtype)
 
 
+def dequantize_zp_float(q: np.ndarray, scales: np.ndarray, zeros: np.ndarray, group_size: int,
+                        dtype: str) -> np.ndarray:
+    """HQQ-style float zero-points: w[k, n] = dtype( dtype(q[k, n] - zp[g, n]) * s[g, n] ), the
+    arithmetic of the reference's test (tests/kernels/quantization/test_marlin_gemm.py:520-525:
+    ``(b_flat - zp_flat) * s_flat`` in 16-bit tensors).  The CUDA kernels compute
+    q * s - dtype(zp * s) with one fma (marlin_template.h:174-181,1235-1240); the two agree
+    within the GEMM tolerance."""
+    K = q.shape[0]
+    g = np.arange(K, dtype=np.int64) // group_size
+    z = round_to_dtype(zeros.astype(np.float32), dtype)[g, :]
+    s = round_to_dtype(scales.astype(np.float32), dtype)[g, :]
+    centred = round_to_dtype(q.astype(np.float32) - z, dtype)
+    return round_to_dtype(centred * s, dtype)
+
+
 def gemm_ref(a: np.ndarray, w: np.ndarray, bias: np.ndarray | None = None) -> np.ndarray:
     """fp32-accumulated product of 16-bit operands held as float32."""
     out = a.astype(np.float32) @ w.astype(np.float32)

@@ -1,7 +1,8 @@
 """Generate the golden fixtures in this directory from the reference's own
 Python packers (CPU only).
 
-Usage:  python tests/golden/make_golden.py <path-to-reference-checkout>
+Usage:  python tests/golden/make_golden.py <path-to-reference-checkout> [hqq]
+        (with `hqq` only the float zero-point fixture is rewritten)
 
 The reference checkout is only needed to (re)generate the fixtures; the tests
 read the committed ``*.npz`` files and never import the reference.  All inputs
@@ -19,6 +20,10 @@ inputs):
   gemm_*.npz         marlin_quantize / awq_marlin_quantize outputs (w_ref,
                      Marlin weights, scales, zero-points, g_idx, sort indices),
                      an activation matrix and the fp32 product a @ w_ref
+  hqq_u4_g64_f16.npz float zero-points (HQQ): codes, scales, zero-points, their Marlin
+                     forms from gptq_pack / marlin_weights / marlin_permute_scales, and
+                     the dequantised weights and product computed as the reference's
+                     test does (tests/kernels/quantization/test_marlin_gemm.py:463-534)
 """
 
 import os
@@ -33,7 +38,33 @@ def _bits16(t):
     return t.contiguous().view(torch.int16).numpy().view(np.uint16).copy()
 
 
-def main(ref_root: str) -> None:
+def make_hqq(here, mu, mt, qu) -> None:
+    import torch
+    torch.manual_seed(7)
+    M, K, N, g = 19, 256, 128, 64
+    a = torch.randn((M, K), dtype=torch.float16)
+    b_weight = torch.randint(0, 10, (N, K), dtype=torch.uint8)            # [N, K] as in the test
+    scale = torch.randn((N, K // g), dtype=torch.float16)
+    zero = torch.randn((N, K // g), dtype=torch.float16)
+    q_kn = b_weight.transpose(1, 0).contiguous().to(torch.int32)          # [K, N]
+    gptq_w_q = qu.gptq_pack(q_kn, 4, K, N)
+    marlin_q = mt.marlin_weights(q_kn, K, N, 4, mt.get_weight_perm(4))    # what the repack op returns
+    marlin_s = mu.marlin_permute_scales(scale.transpose(1, 0).contiguous(), K, N, g)
+    marlin_zp = mu.marlin_permute_scales(zero.transpose(1, 0).contiguous(), K, N, g)
+    b_flat = b_weight.reshape(-1, g)
+    dequant = (b_flat - zero.reshape(-1, 1)) * scale.reshape(-1, 1)       # fp16 arithmetic
+    w_ref = dequant.reshape(b_weight.shape).transpose(1, 0).contiguous()  # [K, N]
+    np.savez_compressed(
+        os.path.join(here, "hqq_u4_g64_f16.npz"),
+        M=np.int64(M), K=np.int64(K), N=np.int64(N), group_size=np.int64(g),
+        a_bits=_bits16(a), q=q_kn.numpy(), gptq_in=gptq_w_q.numpy(), marlin_q_w=marlin_q.numpy(),
+        scale_bits=_bits16(scale.transpose(1, 0).contiguous()),
+        zero_bits=_bits16(zero.transpose(1, 0).contiguous()),
+        marlin_s_bits=_bits16(marlin_s), marlin_zp_bits=_bits16(marlin_zp),
+        w_ref_bits=_bits16(w_ref), out_ref=(a.float() @ w_ref.float()).numpy())
+
+
+def main(ref_root: str, only: str | None = None) -> None:
     sys.path.insert(0, ref_root)
     import torch
     from vllm.model_executor.layers.quantization.utils import marlin_utils as mu
@@ -42,6 +73,10 @@ def main(ref_root: str) -> None:
     from vllm.scalar_type import scalar_types
 
     here = os.path.dirname(os.path.abspath(__file__))
+    if only == "hqq":
+        make_hqq(here, mu, mt, qu)
+        print("hqq fixture written to", here)
+        return
     types = {"uint4b8": scalar_types.uint4b8, "uint4": scalar_types.uint4,
              "uint8b128": scalar_types.uint8b128, "uint8": scalar_types.uint8}
 
@@ -128,10 +163,11 @@ def main(ref_root: str) -> None:
         rec["marlin_s_bits"] = _bits16(ms)
         rec["out_ref"] = (a.float() @ w_ref.float()).numpy()
         np.savez_compressed(os.path.join(here, f"gemm_{name}.npz"), **rec)
+    make_hqq(here, mu, mt, qu)
     print("golden fixtures written to", here)
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
+    if len(sys.argv) not in (2, 3):
         sys.exit(__doc__)
-    main(sys.argv[1])
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

@@ -132,3 +132,20 @@ def test_bf16_rounding_helper():
     import torch
     want = torch.from_numpy(x).bfloat16().float().numpy()
     assert np.array_equal(mo.round_to_bf16(x), want)
+
+
+def test_hqq_float_zero_points_match_reference():
+    """Float zero-points: packers, scale-layout permutation of the zero-points, and the
+    dequantised weights / product of the reference's test formula."""
+    g = _load("hqq_u4_g64_f16.npz")
+    K, N, gs = int(g["K"]), int(g["N"]), int(g["group_size"])
+    q = g["q"]
+    assert np.array_equal(mo.gptq_pack(q, 4), g["gptq_in"])
+    assert np.array_equal(mo.gptq_marlin_repack(g["gptq_in"], None, K, N, 4), g["marlin_q_w"])
+    s, z = _f16(g["scale_bits"], False), _f16(g["zero_bits"], False)
+    assert np.array_equal(mo.marlin_permute_scales(s, K, N, gs), _f16(g["marlin_s_bits"], False))
+    assert np.array_equal(mo.marlin_permute_scales(z, K, N, gs), _f16(g["marlin_zp_bits"], False))
+    w = mo.dequantize_zp_float(q, s, z, gs, "float16")
+    assert np.array_equal(w, _f16(g["w_ref_bits"], False))
+    out = mo.gemm_ref(_f16(g["a_bits"], False), w)
+    assert np.allclose(out, g["out_ref"], rtol=1e-5, atol=1e-4)

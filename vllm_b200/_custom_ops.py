@@ -256,14 +256,18 @@ def _gptq_marlin_gemm_cuda(a, c_or_none, b_q_weight, b_bias_or_none, b_scales, g
             zeros = b_zeros_or_none
     if zeros is not None:
         _check(qt.bias == 0, f"b_q_type must be u4 or u8 when has_zp = True. Got = {qt}")
-        if is_zp_float:
-            raise NotImplementedError("float zero-points (is_zp_float) are not supported")
         _check(zeros.dim() == 2, f"b_zeros rank = {zeros.dim()} is not 2")
         _check(zeros.size(0) == num_groups,
                f"b_zeros dim 0 = {zeros.size(0)} is not num_groups = {num_groups}")
-        _check(zeros.size(1) == size_n // pf,
-               f"b_zeros dim 1 = {zeros.size(1)} is not size_n / pack_factor = {size_n // pf}")
-        _check(zeros.dtype == torch.int32, "b_zeros must be int32")
+        if is_zp_float:
+            _check(a.dtype == torch.float16,
+                   "Computation type must be float16 (half) when using float zero points.")
+            _check(zeros.size(1) == size_n, f"b_zeros dim 1 = {zeros.size(1)} is not size_n = {size_n}")
+            _check(zeros.dtype == a.dtype, "float zero-points must have the dtype of a")
+        else:
+            _check(zeros.size(1) == size_n // pf,
+                   f"b_zeros dim 1 = {zeros.size(1)} is not size_n / pack_factor = {size_n // pf}")
+            _check(zeros.dtype == torch.int32, "b_zeros must be int32")
     else:
         _check(qt.bias != 0,
                "b_q_type must be uint4b8, uint8b128, float8_e4m3fn or float4_e2m1f when "
@@ -280,7 +284,8 @@ def _gptq_marlin_gemm_cuda(a, c_or_none, b_q_weight, b_bias_or_none, b_scales, g
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=a.device)
         flags = ((_lib.FLAG_K_FULL if is_k_full else 0)
                  | (_lib.FLAG_ATOMIC_ADD if use_atomic_add else 0)
-                 | (_lib.FLAG_FP32_REDUCE if use_fp32_reduce else 0))
+                 | (_lib.FLAG_FP32_REDUCE if use_fp32_reduce else 0)
+                 | (_lib.FLAG_ZP_FLOAT if (is_zp_float and zeros is not None) else 0))
         args = (_ptr(a), a.stride(0), _ptr(b_q_weight), _ptr(b_scales), _ptr(zeros), _ptr(g_idx),
                 _ptr(perm), _ptr(bias), _ptr(c), _ptr(scratch), nbytes, _ptr(workspace),
                 workspace.numel(), b_q_type, _lib.BF16 if a.dtype == torch.bfloat16 else _lib.F16,

@@ -190,8 +190,9 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
                 "b_q_type must be u4 or u8 when has_zp = True");
   B200Q_REQUIRE(has_zp || !type_has_zp, B200Q_EINVAL,
                 "b_q_type must be uint4b8 or uint8b128 when has_zp = False");
-  B200Q_REQUIRE(!(flags & B200Q_FLAG_ZP_FLOAT), B200Q_EUNSUPPORTED,
-                "float zero-points (is_zp_float) are not supported");
+  const bool zp_float = has_zp && (flags & B200Q_FLAG_ZP_FLOAT);
+  B200Q_REQUIRE(!zp_float || a_dtype == B200Q_F16, B200Q_EINVAL,
+                "Computation type must be float16 (half) when using float zero points.");
   B200Q_REQUIRE(a_dtype == B200Q_F16 || a_dtype == B200Q_BF16, B200Q_EINVAL,
                 "gpt_marlin_gemm only supports bfloat16 and float16");
   // ---- shapes ------------------------------------------------------------------------
@@ -277,8 +278,11 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     lda_used = size_k;
   }
 
+  if (zp_float)
+    B200Q_REQUIRE(gm == kGrouped && !has_act_order, B200Q_EUNSUPPORTED,
+                  "float zero-points need grouped scales without act_order");
   // ---- prefill regime: tensor-core kernel ----------------------------------------------
-  if (tc_path_enabled() && group_blocks >= 2 && tc_gemm_supported(size_m, size_n, size_k, gm)) {
+  if (!zp_float && tc_path_enabled() && group_blocks >= 2 && tc_gemm_supported(size_m, size_n, size_k, gm)) {
     int rc = launch_tc_gemm(a_used, lda_used, b_q_weight, b_scales, b_zeros, b_bias, c, a_dtype,
                             bits, size_m, size_n, size_k, group_blocks, gm == kChannel, scratch,
                             (int64_t)((scratch_bytes - a_tmp_bytes) / 256 * 256), stream);
@@ -286,7 +290,7 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     return launch_all_reduce(*link, c, c, size_m * size_n, a_dtype, stream);
   }
   // one decode launch of the streaming kernel covers the problem: it all-reduces itself
-  const bool fuse_ar = link && size_m <= 32 && gm != kLookup && fused_ar_enabled();
+  const bool fuse_ar = link && size_m <= 32 && gm != kLookup && !zp_float && fused_ar_enabled();
 
   // ---- decode regime: chunks of up to 64 rows --------------------------------------------
   const int nt = (int)(size_n / 64);
@@ -297,7 +301,7 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     int mb = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
     // slice width in 64-column tiles: two where the accumulators fit in registers
     int ntw = 1;
-    if (nt % 2 == 0) {
+    if (nt % 2 == 0 && !zp_float) {
       if (gm == kChannel && mb <= 4) ntw = 2;
       if (gm == kGrouped && mb <= 2) ntw = grouped_ntw();
     }
@@ -319,6 +323,7 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     p.slices = nt / ntw;
     p.group_blocks = group_blocks;
     p.num_groups = (int)num_groups;
+    p.zp_float = zp_float ? 1 : 0;
     p.ar = ArLink{};
     if (fuse_ar) p.ar = *link;
     int rc;

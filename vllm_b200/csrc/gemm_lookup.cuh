@@ -11,14 +11,15 @@
 
 namespace b200q {
 
-template <int BITS, bool HAS_ZP, int GM, int MB, int NTW>
+// ZPF: the zero-points are 16-bit floats [G, N] in the scales' layout (HQQ) instead of packed codes.
+template <int BITS, bool HAS_ZP, int GM, int MB, int NTW, bool ZPF = false>
 struct LookupCfg {
   static constexpr int kTileBytes = 16 * 64 * BITS / 8;                  // one weight tile
   static constexpr int kWOff = 0;
   static constexpr int kAOff = kWOff + NTW * kTileBytes;                 // MB x 512 B
   static constexpr int kSOff = kAOff + MB * 512;                         // NTW x 128 B scales
   static constexpr int kZOff = kSOff + (GM == kGrouped ? NTW * 128 : 0); // NTW x (32|64) B zeros
-  static constexpr int kZBytes = HAS_ZP ? NTW * 8 * BITS : 0;
+  static constexpr int kZBytes = ZPF ? NTW * 128 : (HAS_ZP ? NTW * 8 * BITS : 0);
   static constexpr int kStageBytes = (kZOff + kZBytes + 127) / 128 * 128;
   // ring depth: as deep as ~96 KB of shared memory per CTA allows, 3..8 stages
   static constexpr int kDepthFit = 96 * 1024 / (kStageBytes * kStreamWarps);
@@ -32,9 +33,10 @@ struct LookupCfg {
   static constexpr int kSlotFloats = MB * 16 * 64 * NTW;
 };
 
-template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, int MINB>
+template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, int MINB, bool ZPF = false>
 __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const StreamParams p) {
-  using Cfg = LookupCfg<BITS, HAS_ZP, GM, MB, NTW>;
+  static_assert(!ZPF || (HAS_ZP && GM == kGrouped), "float zero-points come with grouped scales");
+  using Cfg = LookupCfg<BITS, HAS_ZP, GM, MB, NTW, ZPF>;
   constexpr int D = Cfg::kDepth;
   static_assert(D >= 2, "ring too shallow");
   extern __shared__ __align__(128) unsigned char smem[];
@@ -117,7 +119,12 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
           const int g = kt / p.group_blocks;
           if (GM == kGrouped && lane < NTW * 8)
             cp_async16(st + Cfg::kSOff + lane * 16, S + (size_t)g * p.n + nt0 * 64 + lane * 8);
-          if (HAS_ZP) {
+          if (ZPF) {
+            if (lane < NTW * 8)
+              cp_async16(st + Cfg::kZOff + lane * 16,
+                         reinterpret_cast<const uint16_t*>(p.zeros) + (size_t)g * p.n + nt0 * 64 +
+                             lane * 8);
+          } else if (HAS_ZP) {
             constexpr int kChunks = NTW * 8 * BITS / 16;  // 16 B chunks of zero-point words
             if (lane < kChunks)
               cp_async16(st + Cfg::kZOff + lane * 16,
@@ -146,7 +153,17 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
             sdup[j][2 * sub + 1] = dup_hi(sv[sub]);
           }
         }
-        if (HAS_ZP) {
+        if (ZPF) {
+          // -(zero-point * scale), rounded once like the reference's __hmul2
+          // (marlin_template.h:1235-1240); the weights then take one fma each
+          const uint4 z4 = lds128(st + Cfg::kZOff + j * 128 + c8 * 16);
+          const uint32_t zv[4] = {z4.x, z4.y, z4.z, z4.w};
+#pragma unroll
+          for (int sub = 0; sub < 4; ++sub) {
+            zdup[j][2 * sub] = Pair<T>::mul(dup_lo(zv[sub]), sdup[j][2 * sub]) ^ 0x80008000u;
+            zdup[j][2 * sub + 1] = Pair<T>::mul(dup_hi(zv[sub]), sdup[j][2 * sub + 1]) ^ 0x80008000u;
+          }
+        } else if (HAS_ZP) {
           uint32_t zp[4];
           if (BITS == 4) {
             dequant4<T, false>(lds32(st + Cfg::kZOff + j * 32 + c8 * 4), zp);
@@ -223,13 +240,21 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
             dequant8<T, !HAS_ZP>(w[2 * sub + 1], t1);
             f[0] = t0[0]; f[1] = t0[1]; f[2] = t1[0]; f[3] = t1[1];
           }
-          if (HAS_ZP) {
+          if (ZPF) {
+            // q * s - zp * s (scale_and_sub, marlin_template.h:174-181)
+            f[0] = Pair<T>::fma(f[0], sdup[j][2 * sub], zdup[j][2 * sub]);
+            f[1] = Pair<T>::fma(f[1], sdup[j][2 * sub], zdup[j][2 * sub]);
+            f[2] = Pair<T>::fma(f[2], sdup[j][2 * sub + 1], zdup[j][2 * sub + 1]);
+            f[3] = Pair<T>::fma(f[3], sdup[j][2 * sub + 1], zdup[j][2 * sub + 1]);
+          } else if (HAS_ZP) {
             f[0] = Pair<T>::sub(f[0], zdup[j][2 * sub]);
             f[1] = Pair<T>::sub(f[1], zdup[j][2 * sub]);
             f[2] = Pair<T>::sub(f[2], zdup[j][2 * sub + 1]);
             f[3] = Pair<T>::sub(f[3], zdup[j][2 * sub + 1]);
           }
-          if (GM == kGrouped) {
+          if (ZPF) {
+            // scaled by the fma above
+          } else if (GM == kGrouped) {
             f[0] = Pair<T>::mul(f[0], sdup[j][2 * sub]);
             f[1] = Pair<T>::mul(f[1], sdup[j][2 * sub]);
             f[2] = Pair<T>::mul(f[2], sdup[j][2 * sub + 1]);
@@ -371,11 +396,11 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
 }
 
 // Host launcher for one (type, bits, zp, group mode, MB, NTW) variant.
-template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW>
+template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, bool ZPF = false>
 int launch_lookup(const StreamParams& p, int max_ctas, cudaStream_t stream) {
-  using Cfg = LookupCfg<BITS, HAS_ZP, GM, MB, NTW>;
+  using Cfg = LookupCfg<BITS, HAS_ZP, GM, MB, NTW, ZPF>;
   constexpr int kMinBlocks = (MB * NTW <= 2 && Cfg::kSmemBytes <= 112 * 1024) ? 2 : 1;
-  auto kernel = gemm_lookup_kernel<T, BITS, HAS_ZP, GM, MB, NTW, kMinBlocks>;
+  auto kernel = gemm_lookup_kernel<T, BITS, HAS_ZP, GM, MB, NTW, kMinBlocks, ZPF>;
   static bool attr_done[64] = {};  // per device; benign race: the call is idempotent
   int dev = 0;
   B200Q_CUDA_OK(cudaGetDevice(&dev));

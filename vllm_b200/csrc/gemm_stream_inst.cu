@@ -54,6 +54,18 @@ int grouped(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_
   return B200Q_EUNSUPPORTED;
 }
 
+// float zero-points (HQQ): the reference-order kernel for every row count
+int grouped_zp_float(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
+  if (ntw != 1) return B200Q_EUNSUPPORTED;
+  const int mb = (rows8 + 1) / 2;  // 16-row blocks
+  switch (mb) {
+    case 1: return launch_lookup<T, B, true, kGrouped, 1, 1, true>(p, max_ctas, stream);
+    case 2: return launch_lookup<T, B, true, kGrouped, 2, 1, true>(p, max_ctas, stream);
+    case 4: return launch_lookup<T, B, true, kGrouped, 4, 1, true>(p, max_ctas, stream);
+  }
+  return B200Q_EUNSUPPORTED;
+}
+
 int lookup(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
   if (ntw != 1) return B200Q_EUNSUPPORTED;
   const int mb = (rows8 + 1) / 2;  // 16-row blocks
@@ -70,6 +82,9 @@ int lookup(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t
 template <>
 int dispatch_stream<InstT, INST_BITS>(const StreamParams& p, bool has_zp, int gm, int mb, int ntw,
                                       int max_ctas, cudaStream_t stream) {
+  if (p.zp_float)
+    return (has_zp && gm == kGrouped) ? grouped_zp_float(p, mb, ntw, max_ctas, stream)
+                                      : B200Q_EUNSUPPORTED;
   if (gm == kChannel)
     return has_zp ? channel<true>(p, mb, ntw, max_ctas, stream)
                   : channel<false>(p, mb, ntw, max_ctas, stream);
