@@ -2,9 +2,14 @@
 // 16-bit and multiplied by their scale before the MMA.  This is the general
 // path; it is used for act-order layers that hold a partial K range, where the
 // scale group of every row comes from g_idx (group lookup) and so cannot be
-// factored out of the MMA.  The grouped / channel-wise cases run the faster
-// kernel of gemm_stream.cuh; work decomposition, ring and reduction are the
-// same and are described there.
+// factored out of the MMA, for float zero-points (HQQ), and for 33..64-row
+// launches the tensor-core kernel cannot take.  The grouped / channel-wise
+// decode cases run the faster kernel of gemm_stream.cuh.
+//
+// Work decomposition: the (column slice, k-tile) space is cut into equal stripes,
+// one per CTA; a CTA whose stripe covers part of a slice leaves fp32 partial sums
+// in the scratch and the last CTA to arrive at a slice (counter in the workspace,
+// reset on the way out) adds them up and writes C.
 #pragma once
 
 #include "gemm_params.cuh"

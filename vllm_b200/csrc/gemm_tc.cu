@@ -1,5 +1,5 @@
 // Prefill-regime mixed-precision GEMM on the 5th-generation tensor cores:
-// C[M,N] = A[M,K] * dequant(B) for M > 64, tcgen05.mma with TMEM accumulators.
+// C[M,N] = A[M,K] * dequant(B) from 33 rows up, tcgen05.mma with TMEM accumulators.
 //
 // One persistent CTA per SM walks over BM x BN output tiles (BM, BN in {128,
 // 256}; m fastest so that CTAs running together share weight tiles).  The k
@@ -20,6 +20,11 @@
 //   4 epilogue warps tcgen05.ld the finished accumulator, add bias, convert and
 //                   store C; when two accumulator sets fit in TMEM (all but
 //                   256 x 256) the MMA warp meanwhile fills the other one.
+//
+// Problems with fewer tiles than SMs split K: a work item is (tile, share of the k
+// range), items leave fp32 partials in the caller's scratch and splitk_reduce_kernel
+// adds them in split order (plan_tiles picks tile shape and split from measured
+// per-step times).
 //
 // All hand-offs are mbarriers.  Every wait is bounded: after kSpinLimit polls
 // a role records an error code in g_tc_error, stops waiting and lets the
