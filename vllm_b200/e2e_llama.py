@@ -8,7 +8,9 @@ order, the four projections per block and the (hidden, residual) hand-over betwe
 blocks follow the reference's model (vllm/model_executor/models/llama.py:73-347).
 The residual add + RMSNorm and SiLU * mul steps next to the projections run through
 this package's kernels; after a row-parallel projection the all-reduce is either
-inside the GEMM kernel (up to 32 rows) or inside the add + RMSNorm kernel.  Embedding and lm_head stay 16-bit
+inside the GEMM kernel (up to 32 rows) or inside the add + RMSNorm kernel.
+Attention is library code: flash_attn's kv-cache kernel (rotary embedding, cache
+append and attention in one launch) when the package is importable, else torch SDPA.  Embedding and lm_head stay 16-bit
 and replicated (the reference quantizes lm_head only when the checkpoint says
 so, gptq_marlin.py:198).  Attention, norms and sampling use stock torch ops: they
 are outside the hot path this package replaces.
@@ -19,6 +21,11 @@ from dataclasses import dataclass
 
 import torch
 import torch.nn.functional as F
+
+try:  # library attention kernel; the torch path below is the fall-back
+    from flash_attn import flash_attn_with_kvcache as _fa_kvcache
+except Exception:  # pragma: no cover - depends on the image
+    _fa_kvcache = None
 
 from . import _custom_ops as ops
 from . import distributed as D
@@ -100,6 +107,15 @@ class DecoderLayer(torch.nn.Module):
         qkv = self.qkv_proj(x.view(B * T, -1)).view(B, T, -1)
         q, k, v = qkv.split([self.n_q * cfg.head_dim, self.n_kv * cfg.head_dim,
                              self.n_kv * cfg.head_dim], dim=-1)
+        if isinstance(pos_index, dict):
+            # flash_attn: caches are [B, S, kv heads, D]; rotary, append at seqlens, attention
+            fa = pos_index
+            attn = _fa_kvcache(q.view(B, T, self.n_q, cfg.head_dim), k_cache, v_cache,
+                               k=k.view(B, T, self.n_kv, cfg.head_dim),
+                               v=v.view(B, T, self.n_kv, cfg.head_dim), rotary_cos=fa["cos"],
+                               rotary_sin=fa["sin"], cache_seqlens=fa["seqlens"], causal=True,
+                               rotary_interleaved=False)
+            return self._mlp_tail(attn.reshape(B * T, -1), residual, next_norm, B, T)
         q = q.view(B, T, self.n_q, cfg.head_dim).transpose(1, 2)
         k = k.view(B, T, self.n_kv, cfg.head_dim).transpose(1, 2)
         v = v.view(B, T, self.n_kv, cfg.head_dim).transpose(1, 2)
@@ -113,7 +129,9 @@ class DecoderLayer(torch.nn.Module):
             v_cache.index_copy_(2, pos_index, v)
             attn = F.scaled_dot_product_attention(q, k_cache, v_cache, attn_mask=attn_mask,
                                                   enable_gqa=True)
-        attn = attn.transpose(1, 2).reshape(B * T, -1)
+        return self._mlp_tail(attn.transpose(1, 2).reshape(B * T, -1), residual, next_norm, B, T)
+
+    def _mlp_tail(self, attn, residual, next_norm, B, T):
         h = self._row_parallel_then_norm(self.o_proj, attn, residual, self.post_norm)
         gu = self.gate_up_proj(h)
         act = torch.empty((B * T, gu.shape[-1] // 2), dtype=gu.dtype, device=gu.device)
@@ -131,7 +149,8 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 
 class LlamaDecoder(torch.nn.Module):
     def __init__(self, cfg: LlamaConfig, max_seq: int, batch: int, dtype=torch.bfloat16,
-                 device="cuda", seed: int = 0, tp_rank: int = 0, tp_size: int = 1):
+                 device="cuda", seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
+                 use_flash_attn: bool = True):
         super().__init__()
         self.cfg, self.max_seq, self.batch = cfg, max_seq, batch
         gen = torch.Generator(device=device).manual_seed(seed)       # same weights on every rank
@@ -146,18 +165,27 @@ class LlamaDecoder(torch.nn.Module):
             DecoderLayer(cfg, qc, dtype, device, gen_shard, tp_rank, tp_size)
             for _ in range(cfg.num_layers))
         n_kv = self.layers[0].n_kv
-        self.k_cache = [torch.zeros(batch, n_kv, max_seq, cfg.head_dim, dtype=dtype, device=device)
+        self.use_fa = _fa_kvcache is not None and use_flash_attn
+        cache_shape = ((batch, max_seq, n_kv, cfg.head_dim) if self.use_fa
+                       else (batch, n_kv, max_seq, cfg.head_dim))
+        self.k_cache = [torch.zeros(cache_shape, dtype=dtype, device=device)
                         for _ in range(cfg.num_layers)]
         self.v_cache = [torch.zeros_like(k) for k in self.k_cache]
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=device).float()
                                         / cfg.head_dim))
         ang = torch.arange(max_seq, device=device).float()[:, None] * inv[None]
         self.cos, self.sin = ang.cos(), ang.sin()
+        self.fa = {"cos": self.cos.to(dtype), "sin": self.sin.to(dtype),
+                   "seqlens": torch.zeros(batch, dtype=torch.int32, device=device)}
 
     @torch.no_grad()
     def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
         """tokens [B, T] -> next token ids [B]."""
         B, T = tokens.shape
+        if self.use_fa:
+            self.fa["seqlens"].zero_()
+            x = self._run_layers(self.embed[tokens], None, None, self.fa, None, T)
+            return (x[:, -1] @ self.lm_head.t()).argmax(-1)
         x = self._run_layers(self.embed[tokens], self.cos[:T], self.sin[:T], None, None, T)
         return (x[:, -1] @ self.lm_head.t()).argmax(-1)
 
@@ -180,6 +208,10 @@ class LlamaDecoder(torch.nn.Module):
                     attn_mask: torch.Tensor) -> torch.Tensor:
         """One token per sequence.  tokens [B]; pos_index int64 [1] (cache slot to write);
         attn_mask bool [1, 1, 1, max_seq] with the valid cache slots set."""
+        if self.use_fa:
+            self.fa["seqlens"].copy_(pos_index.to(torch.int32).expand(tokens.shape[0]))
+            x = self._run_layers(self.embed[tokens][:, None], None, None, self.fa, None, 0)
+            return (x[:, 0] @ self.lm_head.t()).argmax(-1)
         cos, sin = self.cos.index_select(0, pos_index), self.sin.index_select(0, pos_index)
         x = self._run_layers(self.embed[tokens][:, None], cos, sin, pos_index, attn_mask, 0)
         return (x[:, 0] @ self.lm_head.t()).argmax(-1)
