@@ -353,8 +353,9 @@ def run_ours(args, world, rank, local_rank):
     if dist is not None:
         dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
     ms2 = ms2.tolist()
+    decode = run_decode(world, rank, dev) if os.environ.get("BENCH_NO_DECODE", "0") != "1" else None
     if rank == 0:
-        report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks)
+        report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, decode)
     if dist is not None:
         # CUDA graphs that captured NCCL kernels are still alive: tearing the communicator down
         # under them can block, so leave together and let process exit release everything
@@ -364,7 +365,38 @@ def run_ours(args, world, rank, local_rank):
         os._exit(0)
 
 
-def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks):
+def run_decode(world, rank, dev):
+    """Third part of the metric: greedy decode of a Llama-3-8B-shaped model (random weights, GPTQ
+    uint4b8 g128) whose projections all run through this library, tensor-parallel over the ranks.
+    Batch 64, prompt 512, CUDA-graph decode steps timed with CUDA events, max over ranks."""
+    import torch
+    try:
+        from vllm_b200.e2e_llama import LlamaConfig, LlamaDecoder, generate
+        batch, prompt, new = 64, 512, 64
+        cfg = LlamaConfig()
+        model = LlamaDecoder(cfg, max_seq=prompt + new + 2, batch=batch, device=dev, tp_rank=rank,
+                             tp_size=world)
+        gen = torch.Generator(device=dev).manual_seed(0)
+        prompts = torch.randint(0, cfg.vocab_size, (batch, prompt), device=dev, generator=gen)
+        _, prefill_ms, decode_ms = generate(model, prompts, new + 1, use_graph=True)
+        t = torch.tensor([prefill_ms, decode_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        prefill_ms, decode_ms = t.tolist()
+        del model
+        torch.cuda.empty_cache()
+        return {"metric": "llama3_8b_gptq_decode_tokens_per_s", "value": batch * new / decode_ms * 1e3,
+                "unit": "tokens/s", "ms_per_decode_step": decode_ms / new, "prefill_ms": prefill_ms,
+                "batch": batch, "prompt": prompt, "new_tokens": new, "tensor_parallel": world,
+                "data": "synthetic (random-init weights of the Llama-3-8B architecture)",
+                "note": "projections, residual add + RMSNorm, SiLU*mul and the row-parallel all-reduce "
+                        "are this library's kernels; attention is a library kernel"}
+    except Exception as exc:  # the GEMM sweep above is the primary result
+        return {"error": repr(exc)[:300]}
+
+
+def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, decode=None):
     peaks = load_peaks()
     k_steps = args.steps
     rows = []
@@ -419,6 +451,7 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks):
                         "host memory every call; weights resident (the op takes device tensors)"},
         "gpu_launches": int(launches),
         "clocks": clocks,
+        "decode": decode,
         "per_shape": rows,
     }
     if world == 1:
