@@ -363,6 +363,35 @@ def dequantize_zp_float(q: np.ndarray, scales: np.ndarray, zeros: np.ndarray, gr
     return round_to_dtype(centred * s, dtype)
 
 
+def fp8_e4m3fn_decode(codes: np.ndarray) -> np.ndarray:
+    """float8_e4m3fn bit patterns -> float32: sign, 4 exponent bits (bias 7), 3 mantissa bits, no
+    infinities; exponent 0 is subnormal (m / 8 * 2^-6); 0x7f / 0xff are NaN."""
+    c = codes.astype(np.uint32)
+    sign = np.where(c & 0x80, -1.0, 1.0).astype(np.float32)
+    e = ((c >> 3) & 0xF).astype(np.int32)
+    m = (c & 0x7).astype(np.float32)
+    mag = np.where(e == 0, m / 8.0 * 2.0 ** -6, (1.0 + m / 8.0) * np.exp2((e - 7).astype(np.float32)))
+    out = (sign * mag).astype(np.float32)
+    out[(c & 0x7F) == 0x7F] = np.nan
+    return out
+
+
+def fp8_fuse_exponent_bias(scales: np.ndarray, dtype: str) -> np.ndarray:
+    """marlin_utils_fp8.py:26-37: the kernels move the fp8 exponent field into the 16-bit format
+    without re-biasing; the factor 2^(bias16 - 7) rides on the scales (2^8 fp16, 2^120 bf16)."""
+    factor = np.float32(2.0 ** 8) if dtype == "float16" else np.float32(2.0 ** 120)
+    return round_to_dtype(scales.astype(np.float32) * factor, dtype)
+
+
+def dequantize_fp8(codes: np.ndarray, scales: np.ndarray, group_size: int, dtype: str) -> np.ndarray:
+    """w[k, n] = dtype( dtype(fp8 value) * s[g(k), n] ) (marlin_utils_fp8.py:325-334:
+    ``fp8_weight.to(dtype) * repeated_scales``); `scales` without the fused exponent bias."""
+    K = codes.shape[0]
+    g = np.zeros(K, dtype=np.int64) if group_size in (-1, K) else np.arange(K) // group_size
+    s = round_to_dtype(scales.astype(np.float32), dtype)[g, :]
+    return round_to_dtype(fp8_e4m3fn_decode(codes) * s, dtype)
+
+
 def gemm_ref(a: np.ndarray, w: np.ndarray, bias: np.ndarray | None = None) -> np.ndarray:
     """fp32-accumulated product of 16-bit operands held as float32."""
     out = a.astype(np.float32) @ w.astype(np.float32)

@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory from the reference's own
 Python packers (CPU only).
 
-Usage:  python tests/golden/make_golden.py <path-to-reference-checkout> [hqq]
-        (with `hqq` only the float zero-point fixture is rewritten)
+Usage:  python tests/golden/make_golden.py <path-to-reference-checkout> [hqq|fp8]
+        (with `hqq` / `fp8` only that fixture is rewritten)
 
 The reference checkout is only needed to (re)generate the fixtures; the tests
 read the committed ``*.npz`` files and never import the reference.  All inputs
@@ -24,6 +24,11 @@ inputs):
                      forms from gptq_pack / marlin_weights / marlin_permute_scales, and
                      the dequantised weights and product computed as the reference's
                      test does (tests/kernels/quantization/test_marlin_gemm.py:463-534)
+  fp8_g128_bf16.npz, fp8_gm1_f16.npz
+                     float8_e4m3fn weights: the steps of marlin_quant_fp8_torch
+                     (marlin_utils_fp8.py:321-352) with the CUDA repack op replaced by the CPU
+                     marlin_weights: codes, scales, weight_ref, packed words, Marlin words,
+                     permuted scales with the exponent bias fused in, and the product
 """
 
 import os
@@ -64,6 +69,37 @@ def make_hqq(here, mu, mt, qu) -> None:
         w_ref_bits=_bits16(w_ref), out_ref=(a.float() @ w_ref.float()).numpy())
 
 
+def make_fp8(here, mu, mt) -> None:
+    import torch
+    from vllm.model_executor.layers.quantization.utils import marlin_utils_fp8 as f8
+    torch.manual_seed(11)
+    for name, dtype, g, M, K, N in (("fp8_g128_bf16", torch.bfloat16, 128, 7, 256, 128),
+                                    ("fp8_gm1_f16", torch.float16, -1, 21, 128, 192)):
+        weight = torch.randn((N, K), dtype=dtype)                         # [N, K] as in the reference
+        a = torch.randn((M, K), dtype=dtype)
+        if g != -1:
+            scales = weight.view(N, -1, g).abs().max(-1)[0] / 448
+            rep = scales.repeat_interleave(g, 1)
+        else:
+            scales = weight.view(N, 1, K).abs().max(-1)[0] / 448
+            rep = scales.repeat_interleave(K, 1)
+        fp8_weight = (weight / rep).to(torch.float8_e4m3fn)
+        weight_ref = fp8_weight.to(dtype) * rep
+        packed = f8.pack_fp8_to_int32(fp8_weight, False).T.contiguous()   # [K / 4, N]
+        codes = fp8_weight.view(torch.uint8).T.contiguous()               # [K, N]
+        marlin_q = mt.marlin_weights(codes.to(torch.int32), K, N, 8, mt.get_weight_perm(8))
+        marlin_s = f8.fp8_fused_exponent_bias_into_scales(
+            mu.marlin_permute_scales(scales.T.contiguous(), K, N, g))
+        np.savez_compressed(
+            os.path.join(here, name + ".npz"),
+            M=np.int64(M), K=np.int64(K), N=np.int64(N), group_size=np.int64(g),
+            is_bf16=np.int64(dtype == torch.bfloat16), a_bits=_bits16(a), codes=codes.numpy(),
+            scales_bits=_bits16(scales.T.contiguous()), packed=packed.numpy(),
+            marlin_q_w=marlin_q.numpy(), marlin_s_bits=_bits16(marlin_s),
+            w_ref_bits=_bits16(weight_ref.T.contiguous()),
+            out_ref=(a.float() @ weight_ref.T.float()).numpy())
+
+
 def main(ref_root: str, only: str | None = None) -> None:
     sys.path.insert(0, ref_root)
     import torch
@@ -76,6 +112,10 @@ def main(ref_root: str, only: str | None = None) -> None:
     if only == "hqq":
         make_hqq(here, mu, mt, qu)
         print("hqq fixture written to", here)
+        return
+    if only == "fp8":
+        make_fp8(here, mu, mt)
+        print("fp8 fixtures written to", here)
         return
     types = {"uint4b8": scalar_types.uint4b8, "uint4": scalar_types.uint4,
              "uint8b128": scalar_types.uint8b128, "uint8": scalar_types.uint8}
@@ -164,6 +204,7 @@ def main(ref_root: str, only: str | None = None) -> None:
         rec["out_ref"] = (a.float() @ w_ref.float()).numpy()
         np.savez_compressed(os.path.join(here, f"gemm_{name}.npz"), **rec)
     make_hqq(here, mu, mt, qu)
+    make_fp8(here, mu, mt)
     print("golden fixtures written to", here)
 
 

@@ -149,3 +149,30 @@ def test_hqq_float_zero_points_match_reference():
     assert np.array_equal(w, _f16(g["w_ref_bits"], False))
     out = mo.gemm_ref(_f16(g["a_bits"], False), w)
     assert np.allclose(out, g["out_ref"], rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["fp8_g128_bf16", "fp8_gm1_f16"])
+def test_fp8_weights_match_reference(name):
+    """float8_e4m3fn weights: decode table, packing, Marlin layout, fused-bias scales and the
+    dequantised weights of the reference's marlin_quant_fp8_torch steps."""
+    g = _load(name + ".npz")
+    K, N, gs, bf = int(g["K"]), int(g["N"]), int(g["group_size"]), bool(g["is_bf16"])
+    dtype = "bfloat16" if bf else "float16"
+    codes = g["codes"]
+    assert np.array_equal(mo.pack_rows(codes.astype(np.int32), 8), g["packed"])
+    assert np.array_equal(mo.marlin_weights(codes.astype(np.int32), 8), g["marlin_q_w"])
+    assert np.array_equal(mo.gptq_marlin_repack(g["packed"], None, K, N, 8), g["marlin_q_w"])
+    s = _f16(g["scales_bits"], bf)
+    fused = mo.fp8_fuse_exponent_bias(mo.marlin_permute_scales(s, K, N, gs), dtype)
+    assert np.array_equal(fused, _f16(g["marlin_s_bits"], bf))
+    w = mo.dequantize_fp8(codes, s, gs, dtype)
+    assert np.array_equal(w, _f16(g["w_ref_bits"], bf))
+    out = mo.gemm_ref(_f16(g["a_bits"], bf), w)
+    assert np.allclose(out, g["out_ref"], rtol=1e-5, atol=1e-4)
+
+
+def test_fp8_decode_known_values():
+    c = np.array([0x00, 0x01, 0x07, 0x08, 0x38, 0x7E, 0x80, 0xB8, 0xFE], dtype=np.uint8)
+    want = [0.0, 2.0 ** -9, 7 * 2.0 ** -9, 2.0 ** -6, 1.0, 448.0, -0.0, -1.0, -448.0]
+    assert mo.fp8_e4m3fn_decode(c).tolist() == want
+    assert np.isnan(mo.fp8_e4m3fn_decode(np.array([0x7F, 0xFF], dtype=np.uint8))).all()

@@ -269,7 +269,7 @@ def _gptq_marlin_gemm_cuda(a, c_or_none, b_q_weight, b_bias_or_none, b_scales, g
                    f"b_zeros dim 1 = {zeros.size(1)} is not size_n / pack_factor = {size_n // pf}")
             _check(zeros.dtype == torch.int32, "b_zeros must be int32")
     else:
-        _check(qt.bias != 0,
+        _check(qt.bias != 0 or qt.is_floating_point(),
                "b_q_type must be uint4b8, uint8b128, float8_e4m3fn or float4_e2m1f when "
                f"has_zp = False. Got = {qt}")
 

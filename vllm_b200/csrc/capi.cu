@@ -176,12 +176,14 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
   // ---- type contract ---------------------------------------------------------------
   int bits = 0;
   bool type_has_zp = false;
+  bool w_fp8 = false;
   if (b_q_type_id == kTypeU4B8) { bits = 4; }
   else if (b_q_type_id == kTypeU8B128) { bits = 8; }
   else if (b_q_type_id == kTypeU4) { bits = 4; type_has_zp = true; }
   else if (b_q_type_id == kTypeU8) { bits = 8; type_has_zp = true; }
+  else if (b_q_type_id == kTypeFE4M3fn) { bits = 8; w_fp8 = true; }
   else {
-    set_error("b_q_type id %lld is not supported (uint4b8, uint8b128, uint4, uint8)",
+    set_error("b_q_type id %lld is not supported (uint4b8, uint8b128, uint4, uint8, float8_e4m3fn)",
               (long long)b_q_type_id);
     return B200Q_EUNSUPPORTED;
   }
@@ -189,7 +191,7 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
   B200Q_REQUIRE(!has_zp || type_has_zp, B200Q_EINVAL,
                 "b_q_type must be u4 or u8 when has_zp = True");
   B200Q_REQUIRE(has_zp || !type_has_zp, B200Q_EINVAL,
-                "b_q_type must be uint4b8 or uint8b128 when has_zp = False");
+                "b_q_type must be uint4b8, uint8b128 or float8_e4m3fn when has_zp = False");
   const bool zp_float = has_zp && (flags & B200Q_FLAG_ZP_FLOAT);
   B200Q_REQUIRE(!zp_float || a_dtype == B200Q_F16, B200Q_EINVAL,
                 "Computation type must be float16 (half) when using float zero points.");
@@ -281,8 +283,12 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
   if (zp_float)
     B200Q_REQUIRE(gm == kGrouped && !has_act_order, B200Q_EUNSUPPORTED,
                   "float zero-points need grouped scales without act_order");
+  if (w_fp8)
+    B200Q_REQUIRE(!has_act_order, B200Q_EUNSUPPORTED, "float8_e4m3fn weights with act_order");
+  // these two run the reference-order kernel at every row count
+  const bool general_only = zp_float || w_fp8;
   // ---- prefill regime: tensor-core kernel ----------------------------------------------
-  if (!zp_float && tc_path_enabled() && group_blocks >= 2 && tc_gemm_supported(size_m, size_n, size_k, gm)) {
+  if (!general_only && tc_path_enabled() && group_blocks >= 2 && tc_gemm_supported(size_m, size_n, size_k, gm)) {
     int rc = launch_tc_gemm(a_used, lda_used, b_q_weight, b_scales, b_zeros, b_bias, c, a_dtype,
                             bits, size_m, size_n, size_k, group_blocks, gm == kChannel, scratch,
                             (int64_t)((scratch_bytes - a_tmp_bytes) / 256 * 256), stream);
@@ -290,7 +296,7 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     return launch_all_reduce(*link, c, c, size_m * size_n, a_dtype, stream);
   }
   // one decode launch of the streaming kernel covers the problem: it all-reduces itself
-  const bool fuse_ar = link && size_m <= 32 && gm != kLookup && !zp_float && fused_ar_enabled();
+  const bool fuse_ar = link && size_m <= 32 && gm != kLookup && !general_only && fused_ar_enabled();
 
   // ---- decode regime: chunks of up to 64 rows --------------------------------------------
   const int nt = (int)(size_n / 64);
@@ -301,7 +307,7 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     int mb = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
     // slice width in 64-column tiles: two where the accumulators fit in registers
     int ntw = 1;
-    if (nt % 2 == 0 && !zp_float) {
+    if (nt % 2 == 0 && !general_only) {
       if (gm == kChannel && mb <= 4) ntw = 2;
       if (gm == kGrouped && mb <= 2) ntw = grouped_ntw();
     }
@@ -324,6 +330,7 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     p.group_blocks = group_blocks;
     p.num_groups = (int)num_groups;
     p.zp_float = zp_float ? 1 : 0;
+    p.w_fp8 = w_fp8 ? 1 : 0;
     p.ar = ArLink{};
     if (fuse_ar) p.ar = *link;
     int rc;

@@ -37,6 +37,7 @@ void set_error(const char* fmt, ...);
 constexpr int64_t kTypeU4B8 = 4ll << 8 | 8ll << 17 | 1ll << 50;
 constexpr int64_t kTypeU4 = 4ll << 8 | 1ll << 50;
 constexpr int64_t kTypeU8B128 = 8ll << 8 | 128ll << 17 | 1ll << 50;
+constexpr int64_t kTypeFE4M3fn = 2814749767172868ll;  // float8_e4m3fn (csrc/core/scalar_type.hpp)
 constexpr int64_t kTypeU8 = 8ll << 8 | 1ll << 50;
 
 // bump the process-wide launch counter (b200q_kernel_launches)
@@ -253,6 +254,33 @@ __device__ __forceinline__ void dequant8<__nv_bfloat16, true>(uint32_t q, uint32
 template <>
 __device__ __forceinline__ void dequant8<__nv_bfloat16, false>(uint32_t q, uint32_t (&out)[2]) {
   dequant8_bf16<false>(q, out);
+}
+
+// float8_e4m3fn codes (four per word, Marlin 8-bit layout) to 16-bit pairs: sign and the seven
+// exponent / mantissa bits move into the 16-bit format's fields, which leaves the exponent
+// biased by 2^(bias16 - 7); kFp8Rebias<T> (exact power of two) undoes that.  out[0] = bytes
+// (0, 2), out[1] = bytes (1, 3), as dequant8.  Follows the reference's bit manipulation
+// (csrc/quantization/gptq_marlin/dequant.h:320-395); all 254 finite codes convert exactly,
+// subnormals included.
+template <typename T>
+struct Fp8Cvt;
+template <>
+struct Fp8Cvt<half> {
+  static constexpr int kShift = 1;               // 5 - 4 exponent bits
+  static constexpr uint32_t kRebias = 0x5c005c00u;  // 2^8 as a half pair
+  static constexpr float kRebiasInv = 1.0f / 256.0f;
+};
+template <>
+struct Fp8Cvt<__nv_bfloat16> {
+  static constexpr int kShift = 4;               // 8 - 4 exponent bits
+  static constexpr uint32_t kRebias = 0x7b807b80u;  // 2^120 as a bfloat16 pair
+  static constexpr float kRebiasInv = 7.52316384526264e-37f;  // 2^-120
+};
+template <typename T>
+__device__ __forceinline__ void dequant_fp8(uint32_t q, uint32_t (&out)[2]) {
+  const uint32_t q8 = q << 8;
+  out[0] = (q8 & 0x80008000u) | ((q8 & 0x7f007f00u) >> Fp8Cvt<T>::kShift);
+  out[1] = (q & 0x80008000u) | ((q & 0x7f007f00u) >> Fp8Cvt<T>::kShift);
 }
 
 // Position of output column n inside the 32-column "single" permutation used

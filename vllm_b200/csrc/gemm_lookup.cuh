@@ -38,9 +38,13 @@ struct LookupCfg {
   static constexpr int kSlotFloats = MB * 16 * 64 * NTW;
 };
 
-template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, int MINB, bool ZPF = false>
+// FP8: the 8-bit codes are float8_e4m3fn values; the scales carry the exponent re-bias factor
+// (2^8 for fp16, 2^120 for bf16), as the reference's host code prepares them.
+template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, int MINB, bool ZPF = false,
+          bool FP8 = false>
 __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const StreamParams p) {
   static_assert(!ZPF || (HAS_ZP && GM == kGrouped), "float zero-points come with grouped scales");
+  static_assert(!FP8 || (BITS == 8 && !HAS_ZP && GM != kLookup), "fp8 weights: 8 bits, no zero-points");
   using Cfg = LookupCfg<BITS, HAS_ZP, GM, MB, NTW, ZPF>;
   constexpr int D = Cfg::kDepth;
   static_assert(D >= 2, "ring too shallow");
@@ -241,8 +245,21 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
             dequant4<T, !HAS_ZP>(w[sub], f);
           } else {
             uint32_t t0[2], t1[2];
-            dequant8<T, !HAS_ZP>(w[2 * sub], t0);
-            dequant8<T, !HAS_ZP>(w[2 * sub + 1], t1);
+            if (FP8) {
+              dequant_fp8<T>(w[2 * sub], t0);
+              dequant_fp8<T>(w[2 * sub + 1], t1);
+              if (GM == kChannel) {
+                // bring the values to their true magnitude before the MMA (exact); the
+                // channel scale gives the factor back in the epilogue
+                t0[0] = Pair<T>::mul(t0[0], Fp8Cvt<T>::kRebias);
+                t0[1] = Pair<T>::mul(t0[1], Fp8Cvt<T>::kRebias);
+                t1[0] = Pair<T>::mul(t1[0], Fp8Cvt<T>::kRebias);
+                t1[1] = Pair<T>::mul(t1[1], Fp8Cvt<T>::kRebias);
+              }
+            } else {
+              dequant8<T, !HAS_ZP>(w[2 * sub], t0);
+              dequant8<T, !HAS_ZP>(w[2 * sub + 1], t1);
+            }
             f[0] = t0[0]; f[1] = t0[1]; f[2] = t1[0]; f[3] = t1[1];
           }
           if (ZPF) {
@@ -372,6 +389,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
 #pragma unroll
       for (int e = 0; e < Cfg::kEpt; ++e) {
         cs[e] = (GM == kChannel) ? Pair<T>::to_float(S[single_perm_pos(n_base + e)]) : 1.f;
+        if (FP8 && GM == kChannel) cs[e] *= Fp8Cvt<T>::kRebiasInv;
         bs[e] = p.bias ? Pair<T>::to_float(
                              static_cast<const uint16_t*>(p.bias)[single_perm_pos(n_base + e)])
                        : 0.f;
@@ -401,11 +419,11 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
 }
 
 // Host launcher for one (type, bits, zp, group mode, MB, NTW) variant.
-template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, bool ZPF = false>
+template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, bool ZPF = false, bool FP8 = false>
 int launch_lookup(const StreamParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = LookupCfg<BITS, HAS_ZP, GM, MB, NTW, ZPF>;
   constexpr int kMinBlocks = (MB * NTW <= 2 && Cfg::kSmemBytes <= 112 * 1024) ? 2 : 1;
-  auto kernel = gemm_lookup_kernel<T, BITS, HAS_ZP, GM, MB, NTW, kMinBlocks, ZPF>;
+  auto kernel = gemm_lookup_kernel<T, BITS, HAS_ZP, GM, MB, NTW, kMinBlocks, ZPF, FP8>;
   static bool attr_done[64] = {};  // per device; benign race: the call is idempotent
   int dev = 0;
   B200Q_CUDA_OK(cudaGetDevice(&dev));

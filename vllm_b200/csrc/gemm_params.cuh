@@ -29,6 +29,7 @@ struct StreamParams {
   int group_blocks;        // k-tiles per scale group (kGrouped)
   int num_groups;
   int zp_float;            // zeros holds 16-bit floats [G, N] in the scales' layout
+  int w_fp8;               // the 8-bit codes are float8_e4m3fn values
   // weight-embedding constants of the streaming kernel (filled by its launcher)
   uint32_t c_ex, c_mask_lo, c_mask_hi;
   // when ar.world > 0 the streaming kernel all-reduces its output over the link

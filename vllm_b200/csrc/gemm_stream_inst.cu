@@ -66,6 +66,28 @@ int grouped_zp_float(const StreamParams& p, int rows8, int ntw, int max_ctas, cu
   return B200Q_EUNSUPPORTED;
 }
 
+// float8_e4m3fn weights: the reference-order kernel for every row count
+int fp8_weights(const StreamParams& p, int gm, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
+  if constexpr (B == 8) {
+    if (ntw != 1) return B200Q_EUNSUPPORTED;
+    const int mb = (rows8 + 1) / 2;  // 16-row blocks
+    if (gm == kGrouped) {
+      switch (mb) {
+        case 1: return launch_lookup<T, B, false, kGrouped, 1, 1, false, true>(p, max_ctas, stream);
+        case 2: return launch_lookup<T, B, false, kGrouped, 2, 1, false, true>(p, max_ctas, stream);
+        case 4: return launch_lookup<T, B, false, kGrouped, 4, 1, false, true>(p, max_ctas, stream);
+      }
+    } else if (gm == kChannel) {
+      switch (mb) {
+        case 1: return launch_lookup<T, B, false, kChannel, 1, 1, false, true>(p, max_ctas, stream);
+        case 2: return launch_lookup<T, B, false, kChannel, 2, 1, false, true>(p, max_ctas, stream);
+        case 4: return launch_lookup<T, B, false, kChannel, 4, 1, false, true>(p, max_ctas, stream);
+      }
+    }
+  }
+  return B200Q_EUNSUPPORTED;
+}
+
 int lookup(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
   if (ntw != 1) return B200Q_EUNSUPPORTED;
   const int mb = (rows8 + 1) / 2;  // 16-row blocks
@@ -82,6 +104,7 @@ int lookup(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t
 template <>
 int dispatch_stream<InstT, INST_BITS>(const StreamParams& p, bool has_zp, int gm, int mb, int ntw,
                                       int max_ctas, cudaStream_t stream) {
+  if (p.w_fp8) return has_zp ? B200Q_EUNSUPPORTED : fp8_weights(p, gm, mb, ntw, max_ctas, stream);
   if (p.zp_float)
     return (has_zp && gm == kGrouped) ? grouped_zp_float(p, mb, ntw, max_ctas, stream)
                                       : B200Q_EUNSUPPORTED;

@@ -1,6 +1,6 @@
 """Sub-byte scalar type descriptors with the reference's 64-bit id encoding
 (vllm/scalar_type.py:23-164, csrc/core/scalar_type.hpp:17-157).  Only the
-integer weight types of the quantized linear path are tabulated."""
+weight types the quantized linear path of this package accepts are tabulated."""
 from __future__ import annotations
 
 import functools
@@ -56,6 +56,12 @@ class ScalarType:
         return cls(0, size_bits, False, bias or 0)
 
     @classmethod
+    def float_(cls, exponent: int, mantissa: int, finite_values_only: bool,
+               nan_repr: int) -> "ScalarType":
+        """Non-IEEE float (vllm/scalar_type.py:308-326); always signed, no bias."""
+        return cls(exponent, mantissa, True, 0, finite_values_only, nan_repr)
+
+    @classmethod
     def from_id(cls, type_id: int) -> "ScalarType":
         for t in _ALL:
             if t.id == type_id:
@@ -63,6 +69,9 @@ class ScalarType:
         raise ValueError(f"unknown ScalarType id {type_id}")
 
     def __str__(self) -> str:
+        if self.is_floating_point():
+            return f"float{self.size_bits}_e{self.exponent}m{self.mantissa}" + (
+                "fn" if self._finite_values_only else "")
         s = f"uint{self.size_bits}" if not self.signed else f"int{self.size_bits}"
         return s + (f"b{self.bias}" if self.bias else "")
 
@@ -72,6 +81,9 @@ class scalar_types:
     uint8 = ScalarType.uint(8, None)
     uint4b8 = ScalarType.uint(4, 8)
     uint8b128 = ScalarType.uint(8, 128)
+    # NanRepr.EXTD_RANGE_MAX_MIN = 2 (vllm/scalar_type.py:14-20,338-340)
+    float8_e4m3fn = ScalarType.float_(4, 3, True, 2)
 
 
-_ALL = (scalar_types.uint4, scalar_types.uint8, scalar_types.uint4b8, scalar_types.uint8b128)
+_ALL = (scalar_types.uint4, scalar_types.uint8, scalar_types.uint4b8, scalar_types.uint8b128,
+        scalar_types.float8_e4m3fn)
