@@ -83,3 +83,35 @@ def test_random_shapes(dtype, M, K, N, gs):
                mo.fp8_fuse_exponent_bias(mo.marlin_permute_scales(s, K, N, gs), dtype), M, N, K, dtype)
     mf, mr = H.gemm_errors(got, mo.gemm_ref(a, w))
     assert mf <= H.MAX_ABS_FRAC and mr <= H.MEAN_REL, (mf, mr)
+
+
+@pytest.mark.parametrize("dtype_name,gs", [("bfloat16", 128), ("float16", -1)])
+def test_host_helpers_end_to_end(dtype_name, gs):
+    """marlin_quant_fp8_torch (device repack) + apply_fp8_marlin_linear against a @ weight_ref,
+    and prepare_fp8_layer_for_marlin from an fp8 checkpoint tensor."""
+    import torch
+    from vllm_b200 import marlin_utils as mu
+    from vllm_b200 import marlin_utils_fp8 as f8
+    dtype = getattr(torch, dtype_name)
+    torch.manual_seed(3)
+    N, K, M = 256, 512, 24
+    w = torch.randn((N, K), dtype=dtype, device="cuda")
+    a = torch.randn((M, K), dtype=dtype, device="cuda")
+    w_ref, mq, ms = f8.marlin_quant_fp8_torch(w, gs)
+    ws = mu.marlin_make_workspace_new(a.device)
+    out = f8.apply_fp8_marlin_linear(a, mq, ms, ws, N, K, None)
+    ref = a.float() @ w_ref.float()
+    mf, mr = H.gemm_errors(out.float().cpu().numpy(), ref.cpu().numpy())
+    assert mf <= H.MAX_ABS_FRAC and mr <= H.MEAN_REL, (mf, mr)
+
+    class Layer(torch.nn.Module):
+        pass
+    layer = Layer()
+    layer.output_size_per_partition, layer.input_size_per_partition, layer.orig_dtype = N, K, dtype
+    g = K if gs == -1 else gs
+    scales = w.view(N, -1, g).abs().max(-1)[0] / 448                    # [N, K / g]
+    layer.weight = torch.nn.Parameter((w / scales.repeat_interleave(g, 1)).to(torch.float8_e4m3fn),
+                                      requires_grad=False)              # [N, K] checkpoint layout
+    layer.weight_scale = torch.nn.Parameter(scales.float(), requires_grad=False)
+    f8.prepare_fp8_layer_for_marlin(layer, size_k_first=False)
+    assert torch.equal(layer.weight, mq) and torch.equal(layer.weight_scale, ms)

@@ -59,6 +59,27 @@ def test_scalar_types():
     assert (scalar_types.uint4.min(), scalar_types.uint4.max()) == (0, 15)
     assert ScalarType.from_id(mo.UINT8B128_ID) is scalar_types.uint8b128
     assert scalar_types.uint4b8.size_bits == 4 and str(scalar_types.uint4b8) == "uint4b8"
+    # float8_e4m3fn: the id the reference's ScalarType.float_(4, 3, True, EXTD_RANGE_MAX_MIN) yields
+    f8 = scalar_types.float8_e4m3fn
+    assert f8.id == 2814749767172868 and f8.size_bits == 8 and f8.is_floating_point()
+    assert ScalarType.from_id(f8.id) is f8 and str(f8) == "float8_e4m3fn"
+
+
+def test_fp8_host_helpers_match_oracle():
+    from vllm_b200 import marlin_utils_fp8 as f8
+    rng = np.random.default_rng(5)
+    codes = rng.integers(0, 256, size=(64, 32)).astype(np.uint8)            # [K, N]
+    t = torch.from_numpy(codes).view(torch.float8_e4m3fn)
+    assert np.array_equal(f8.pack_fp8_to_int32(t, True).numpy(), mo.pack_rows(codes.astype(np.int32), 8))
+    assert np.array_equal(f8.pack_fp8_to_int32(t.T.contiguous(), False).T.numpy(),
+                          mo.pack_rows(codes.astype(np.int32), 8))
+    for dt, name in ((torch.float16, "float16"), (torch.bfloat16, "bfloat16")):
+        s = torch.from_numpy(rng.uniform(0.002, 0.02, size=(2, 32)).astype(np.float32)).to(dt)
+        got = f8.fp8_fused_exponent_bias_into_scales(s).float().numpy()
+        assert np.array_equal(got, mo.fp8_fuse_exponent_bias(s.float().numpy(), name))
+    finite = codes[(codes & 0x7F) != 0x7F]
+    assert np.array_equal(torch.from_numpy(finite).view(torch.float8_e4m3fn).float().numpy(),
+                          mo.fp8_e4m3fn_decode(finite))
 
 
 def test_torch_permutations_match_oracle():
