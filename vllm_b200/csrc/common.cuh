@@ -172,6 +172,21 @@ __device__ __forceinline__ uint32_t dup_hi(uint32_t x) { return __byte_perm(x, x
 // produced (zero-point types, and the zero-points themselves).
 // Integers up to 2^11 (fp16) / 2^8 (bf16) are exact in the target type, so the
 // "or into the mantissa of 1024.0 / 128.0, then subtract" conversion is exact.
+// (a & mask) | ex as ONE logic instruction.  Written with two immediates the compiler emits
+// two; constants that come out of an opaque move stay in registers and the three-input form
+// takes all of them.
+template <uint32_t V>
+__device__ __forceinline__ uint32_t reg_const() {
+  uint32_t r;
+  asm("mov.u32 %0, %1;\n" : "=r"(r) : "n"(V));
+  return r;
+}
+__device__ __forceinline__ uint32_t mask_or(uint32_t a, uint32_t mask, uint32_t ex) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(d) : "r"(a), "r"(mask), "r"(ex));
+  return d;
+}
+
 template <typename T, bool BIASED>
 __device__ __forceinline__ void dequant4(uint32_t q, uint32_t (&out)[4]);
 
@@ -181,39 +196,43 @@ __device__ __forceinline__ void dequant4<half, true>(uint32_t q, uint32_t (&out)
   const uint32_t SUB = 0x64086408u;  // 1032.0
   const uint32_t MUL = 0x2c002c00u;  // 1/16
   const uint32_t ADD = 0xd480d480u;  // -72.0
-  out[0] = Pair<half>::sub((q & 0x000f000fu) | EX, SUB);
-  out[1] = Pair<half>::fma((q & 0x00f000f0u) | EX, MUL, ADD);
+  const uint32_t ex = reg_const<EX>(), lo = reg_const<0x000f000fu>(), hi = reg_const<0x00f000f0u>();
+  out[0] = Pair<half>::sub(mask_or(q, lo, ex), SUB);
+  out[1] = Pair<half>::fma(mask_or(q, hi, ex), MUL, ADD);
   q >>= 8;
-  out[2] = Pair<half>::sub((q & 0x000f000fu) | EX, SUB);
-  out[3] = Pair<half>::fma((q & 0x00f000f0u) | EX, MUL, ADD);
+  out[2] = Pair<half>::sub(mask_or(q, lo, ex), SUB);
+  out[3] = Pair<half>::fma(mask_or(q, hi, ex), MUL, ADD);
 }
 template <>
 __device__ __forceinline__ void dequant4<half, false>(uint32_t q, uint32_t (&out)[4]) {
   const uint32_t EX = 0x64006400u;
   const uint32_t MUL = 0x2c002c00u;
   const uint32_t ADD = 0xd400d400u;  // -64.0
-  out[0] = Pair<half>::sub((q & 0x000f000fu) | EX, EX);
-  out[1] = Pair<half>::fma((q & 0x00f000f0u) | EX, MUL, ADD);
+  const uint32_t ex = reg_const<EX>(), lo = reg_const<0x000f000fu>(), hi = reg_const<0x00f000f0u>();
+  out[0] = Pair<half>::sub(mask_or(q, lo, ex), EX);
+  out[1] = Pair<half>::fma(mask_or(q, hi, ex), MUL, ADD);
   q >>= 8;
-  out[2] = Pair<half>::sub((q & 0x000f000fu) | EX, EX);
-  out[3] = Pair<half>::fma((q & 0x00f000f0u) | EX, MUL, ADD);
+  out[2] = Pair<half>::sub(mask_or(q, lo, ex), EX);
+  out[3] = Pair<half>::fma(mask_or(q, hi, ex), MUL, ADD);
 }
 template <>
 __device__ __forceinline__ void dequant4<__nv_bfloat16, true>(uint32_t q, uint32_t (&out)[4]) {
   const uint32_t EX = 0x43004300u;   // 128.0
   const uint32_t SUB = 0x43084308u;  // 136.0
+  const uint32_t ex = reg_const<EX>(), lo = reg_const<0x000f000fu>();
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    out[i] = Pair<__nv_bfloat16>::sub((q & 0x000f000fu) | EX, SUB);
+    out[i] = Pair<__nv_bfloat16>::sub(mask_or(q, lo, ex), SUB);
     q >>= 4;
   }
 }
 template <>
 __device__ __forceinline__ void dequant4<__nv_bfloat16, false>(uint32_t q, uint32_t (&out)[4]) {
   const uint32_t EX = 0x43004300u;
+  const uint32_t ex = reg_const<EX>(), lo = reg_const<0x000f000fu>();
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    out[i] = Pair<__nv_bfloat16>::sub((q & 0x000f000fu) | EX, EX);
+    out[i] = Pair<__nv_bfloat16>::sub(mask_or(q, lo, ex), EX);
     q >>= 4;
   }
 }

@@ -32,6 +32,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "gemm_params.cuh"
@@ -173,6 +174,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// st.shared / ld.shared with a compile-time byte offset folded into the instruction
+template <int OFF>
+__device__ __forceinline__ void sts32_off(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u32 [%0+%2], %1;\n" ::"r"(addr), "r"(v), "n"(OFF) : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32_off(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];\n" : "=r"(v) : "r"(addr), "n"(OFF));
+  return v;
 }
 
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B
@@ -380,10 +393,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
     // weights of the stage: [copy][k-tile][tile within the copy]
     const uint32_t w_rel = Cfg::kABytes + Cfg::kBBytes + (nt / Cfg::kCopyTiles) * 4 * Cfg::kCopyRowBytes +
                            kt * Cfg::kCopyRowBytes + (nt % Cfg::kCopyTiles) * Cfg::kTileBytes;
-    uint32_t row_rel[kSubs];
-#pragma unroll
-    for (int si = 0; si < kSubs; ++si)
-      row_rel[si] = Cfg::kABytes + (nt * 64 + (sub0 + si) * 16 + c8) * 128;
+    // converted operand: row of sub-tile sub0 for this lane; the other sub-tiles are 16 rows
+    // (2048 B) further, the second column block 8 rows (1024 B): immediates of the stores
+    const uint32_t b_lo_rel = Cfg::kABytes + (nt * 64 + sub0 * 16 + c8) * 128 + off_lo;
+    const uint32_t b_hi_rel = Cfg::kABytes + (nt * 64 + sub0 * 16 + c8) * 128 + off_hi;
+    // scales of the lane's columns (grouped layout: 16 B per c8 of a tile, 4 B per sub-tile)
+    const uint32_t s_rel = Cfg::kSOff + nt * 128 + c8 * 16 + sub0 * 4;
     uint32_t sbase = smem_base;  // base of the current stage
     // The proxy fence that publishes the converted operand is slow compared with the
     // conversion of one stage; with a ring of four or more stages two stages share one fence.
@@ -410,7 +425,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
         const uint32_t wsrc = sbase + w_rel;
         const uint32_t ssrc = sbase + Cfg::kSOff + slot * Cfg::kSRow;
         const uint32_t zsrc = sbase + Cfg::kZOff + slot * Cfg::kZRow;
-        const uint32_t brow = sbase;
+        const uint32_t b_lo = sbase + b_lo_rel, b_hi = sbase + b_hi_rel;
+        const uint32_t s_lane = sbase + s_rel + slot * Cfg::kSRow;
         sbase = (s + 1 == S) ? smem_base : sbase + Cfg::kStageBytes;
         if (nt < nt_valid) {
           // packed words of this lane for sub-tiles sub0 .. sub0 + kSubs - 1
@@ -439,12 +455,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
               zw[1] = lds32(zsrc + nt * 64 + c8 * 8 + 4);
             }
           }
-#pragma unroll
-          for (int si = 0; si < kSubs; ++si) {
+          // one sub-tile; `si` is a compile-time constant so that the offsets of the scale
+          // load and of the four stores fold into the instructions
+          auto convert_sub = [&](auto si_c, auto cw_c) {
+            constexpr int si = decltype(si_c)::value;
+            constexpr bool kChannelwise = decltype(cw_c)::value;
             const int sub = sub0 + si;
             // scales of columns c8 + 16 sub (low half) and + 8 (high half)
             uint32_t sv;
-            if (p.channelwise) {
+            if constexpr (kChannelwise) {
               // 32-column permutation: column r of a chunk sits at 8 ((r&7)>>1) + 2 (r>>3) + (r&1)
               const int jj = 2 * sub;
               const uint32_t pos = (jj >> 2) * 32 + 8 * (c8 >> 1) + 2 * (jj & 3) + (c8 & 1);
@@ -453,7 +472,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
               asm volatile("ld.shared.u16 %0, [%1];\n" : "=r"(hi) : "r"(ssrc + nt * 128 + pos * 2 + 4));
               sv = lo | (hi << 16);
             } else {
-              sv = lds32(ssrc + nt * 128 + c8 * 16 + sub * 4);
+              sv = lds32_off<si * 4>(s_lane);
             }
             const uint32_t s_lo = dup_lo(sv), s_hi = dup_hi(sv);
             uint32_t f[4];  // (cols c8, k lo), (c8, k hi), (c8 + 8, k lo), (c8 + 8, k hi)
@@ -489,12 +508,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
             f[1] = Pair<T>::mul(f[1], s_lo);
             f[2] = Pair<T>::mul(f[2], s_hi);
             f[3] = Pair<T>::mul(f[3], s_hi);
-            const uint32_t row = brow + row_rel[si];
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_lo), "r"(f[0]) : "memory");
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + off_hi), "r"(f[1]) : "memory");
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_lo), "r"(f[2]) : "memory");
-            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(row + 1024 + off_hi), "r"(f[3]) : "memory");
-          }
+            sts32_off<si * 2048>(b_lo, f[0]);
+            sts32_off<si * 2048>(b_hi, f[1]);
+            sts32_off<si * 2048 + 1024>(b_lo, f[2]);
+            sts32_off<si * 2048 + 1024>(b_hi, f[3]);
+          };
+          // the layout of the scales is a property of the launch: branch once per step, not
+          // per sub-tile (predicated copies of the other layout's loads would still issue)
+          auto convert_all = [&](auto cw_c) {
+            convert_sub(std::integral_constant<int, 0>{}, cw_c);
+            convert_sub(std::integral_constant<int, 1>{}, cw_c);
+            if constexpr (kSubs == 4) {
+              convert_sub(std::integral_constant<int, 2>{}, cw_c);
+              convert_sub(std::integral_constant<int, 3>{}, cw_c);
+            }
+          };
+          if (p.channelwise)
+            convert_all(std::true_type{});
+          else
+            convert_all(std::false_type{});
         }
         if (kPairStages && pending < 0) {
           pending = s;
@@ -539,7 +571,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
       dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
     };
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++tile_i) {
-      const int t = item / KS, ks = item - t * KS;
+      const int t = item / KS;
       const int tn = t / m_tiles, tm = t % m_tiles;
       const int buf = Cfg::kBufs == 2 ? (tile_i & 1) : 0;
       const uint32_t bph = Cfg::kBufs == 2 ? ((tile_i >> 1) & 1) : (tile_i & 1);
