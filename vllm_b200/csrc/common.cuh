@@ -59,6 +59,12 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int sr
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src),
                "r"(src_bytes));
 }
+// The same for a full 16-byte copy, with compile-time byte offsets folded into both addresses.
+template <int DOFF, int SOFF>
+__device__ __forceinline__ void cp_async16_off(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;\n" ::"r"(dst), "l"(src), "n"(DOFF),
+               "n"(SOFF));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

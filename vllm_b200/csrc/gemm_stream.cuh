@@ -276,22 +276,27 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
     int i_first_left = (GM == kGrouped) ? gb - wb % gb : 0;
     int issued = 0;
 
-    uint32_t i_stw = ring;  // next stage to fill with weights (runs ahead only in the prologue)
+    // next stage to fill with weights (runs ahead only in the prologue); the lane's own byte
+    // offset is part of the running address, tile offsets are immediates of the copies
+    const uint32_t w_lane_off = (BITS == 4) ? lane * 16 : (lane & 1) * 512 + (lane >> 1) * 16;
+    uint32_t i_stw = ring + w_lane_off;
+    const uint32_t ring_end_w = ring_end + w_lane_off;
     auto issue_w = [&]() {
-#pragma unroll
-      for (int j = 0; j < NTW; ++j) {
-        if (BITS == 4) {
-          cp_async16(i_stw + j * 512 + lane * 16, i_w + j * 512);
-        } else {
-          // 16 B chunk ch of a tile belongs to lane ch/2, half ch%2
-          cp_async16(i_stw + j * 1024 + (lane & 1) * 512 + (lane >> 1) * 16, i_w + j * 1024);
-          cp_async16(i_stw + j * 1024 + (lane & 1) * 512 + (16 + (lane >> 1)) * 16,
-                     i_w + j * 1024 + 512);
+      if constexpr (BITS == 4) {
+        cp_async16_off<0, 0>(i_stw, i_w);
+        if constexpr (NTW == 2) cp_async16_off<512, 512>(i_stw, i_w);
+      } else {
+        // 16 B chunk ch of a tile belongs to lane ch/2, half ch%2
+        cp_async16_off<0, 0>(i_stw, i_w);
+        cp_async16_off<256, 512>(i_stw, i_w);
+        if constexpr (NTW == 2) {
+          cp_async16_off<1024, 1024>(i_stw, i_w);
+          cp_async16_off<1024 + 256, 1024 + 512>(i_stw, i_w);
         }
       }
       i_w += w_kt_stride;
       i_stw += Cfg::kStageBytes;
-      if (i_stw == ring_end) i_stw = ring;
+      if (i_stw == ring_end_w) i_stw = ring + w_lane_off;
     };
     auto issue_a = [&]() {
 #pragma unroll
