@@ -118,15 +118,28 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize()
         ok &= bool(torch.equal(got_x, want_x)) and bool(torch.equal(got_res, want_res))
     ok &= lib.b200q_device_error(1) == 0
-    q.put((rank, ok))
+    q.put((rank, bool(ok)))
     dist.barrier()
     torch.cuda.synchronize()
     os._exit(0)
 
 
+def _worker_guarded(rank, world, port, q):
+    """Report an exception of the worker instead of dying silently (the parent would otherwise
+    wait for its time-out while the other rank blocks in a collective)."""
+    try:
+        _worker(rank, world, port, q)
+    except BaseException:                      # noqa: BLE001 - everything goes to the parent
+        import traceback
+        q.put((rank, traceback.format_exc()))
+        os._exit(1)
+
+
 @pytest.mark.parametrize("twoshot", [False, True])
 def test_custom_all_reduce_matches_nccl(twoshot, monkeypatch):
     """twoshot: the owner-reduces variant, forced on for every size and for two ranks."""
+    import queue
+
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -138,10 +151,19 @@ def test_custom_all_reduce_matches_nccl(twoshot, monkeypatch):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker_guarded, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=280) for _ in procs]
+    results = []
+    try:
+        for _ in procs:
+            results.append(q.get(timeout=150))
+            if results[-1][1] is not True:       # a failed check or a traceback: stop waiting
+                break
+    except queue.Empty:
+        results.append(("timeout", "no report within 150 s; exit codes %s" % [p.exitcode for p in procs]))
     for p in procs:
-        p.join(timeout=60)
-    assert all(ok for _, ok in results), results
+        p.join(timeout=20)
+        if p.is_alive():
+            p.kill()                             # exactly the children started above
+    assert len(results) == world and all(ok is True for _, ok in results), results
