@@ -119,6 +119,8 @@ def _worker(rank, world, port, q):
         ok &= bool(torch.equal(got_x, want_x)) and bool(torch.equal(got_res, want_res))
     ok &= lib.b200q_device_error(1) == 0
     q.put((rank, bool(ok)))
+    q.close()
+    q.join_thread()          # the feeder thread must flush before os._exit below
     dist.barrier()
     torch.cuda.synchronize()
     os._exit(0)
@@ -132,6 +134,8 @@ def _worker_guarded(rank, world, port, q):
     except BaseException:                      # noqa: BLE001 - everything goes to the parent
         import traceback
         q.put((rank, traceback.format_exc()))
+        q.close()
+        q.join_thread()
         os._exit(1)
 
 
