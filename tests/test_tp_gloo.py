@@ -98,3 +98,52 @@ def test_two_rank_sharding_and_all_reduce(act_order):
         assert p.exitcode == 0
     for rank, err_row, err_col in results:
         assert err_row < 1e-4 and err_col < 1e-4, (rank, err_row, err_col)
+
+
+def _worker_forward(rank, world, port, out_q):
+    """RowParallelLinear.forward on CPU (16-bit weights, torch matmul): with no peer link the
+    fused-reduce scope is inert and the layer falls back to the process group; reduce=False
+    returns the partial sum; the bias is added on rank 0 only."""
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from vllm_b200 import distributed as D
+    from vllm_b200.linear import RowParallelLinear
+    D.initialize_model_parallel(world)
+    scope = D.fused_all_reduce_scope()
+    with scope:
+        pass
+    ok = scope.car is None and scope.done is False
+    torch.manual_seed(0)
+    K, N, M = 64, 32, 3
+    w = torch.randn(N, K)
+    b = torch.randn(N)
+    x = torch.randn(M, K)
+    layer = RowParallelLinear(K, N, bias=True, params_dtype=torch.float32)
+    layer.weight_loader(layer.weight, w)
+    layer.bias.data.copy_(b)
+    k0, k1 = rank * K // world, (rank + 1) * K // world
+    part = layer(x[:, k0:k1], reduce=False)
+    want_part = x[:, k0:k1] @ w[:, k0:k1].t() + (b if rank == 0 else 0)
+    ok &= bool(torch.allclose(part, want_part, atol=1e-5))
+    full = layer(x[:, k0:k1])
+    ok &= bool(torch.allclose(full, x @ w.t() + b, atol=1e-4))
+    whole = RowParallelLinear(K, N, input_is_parallel=False, params_dtype=torch.float32)
+    whole.weight_loader(whole.weight, w)
+    ok &= bool(torch.allclose(whole(x), x @ w.t(), atol=1e-4))
+    out_q.put((rank, bool(ok)))
+    dist.destroy_process_group()
+
+
+def test_row_parallel_forward_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_forward, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok in results), results
