@@ -36,6 +36,7 @@ if ROOT not in sys.path:
 LAYERS = [("qkv", 4096, 6144, False), ("o", 4096, 4096, True),
           ("gate_up", 4096, 28672, False), ("down", 14336, 4096, True)]  # name, K, N, row-parallel
 MS = [1, 4, 16, 64, 256, 1024, 4096]
+MS4 = [1, 16, 128, 1024, 8192]  # BASELINE config 4 (Llama-3-70B shards)
 GROUP = 128
 BITS = 4
 POOL_BYTES = 400_000_000  # per layer: > 3 x the 126 MB L2
@@ -143,7 +144,7 @@ def cpu_sample(layers, m: int, seed: int = 0):
 def run_reference(args, world, rank):
     if rank != 0:
         return
-    layers = [LAYERS[0]]  # bounded sample: the QKV layer at M = 16
+    layers = LAYERS  # bounded sample: the four layers at M = 16, the set cpu_baseline uses
     for _ in range(args.warmup):
         cpu_sample(layers, 16)
     t_bytes, t_s = 0, 0.0
@@ -152,7 +153,8 @@ def run_reference(args, world, rank):
         t_bytes += b
         t_s += s
     value = t_bytes / t_s / 1e9
-    sample = "QKV 4096->6144 at M=16 per step (unpack + act-order dequant + fp32 matmul, numpy)"
+    sample = ("the four layers at M=16 per step (unpack + act-order dequant + fp32 matmul, numpy "
+              "restatement of the reference's CPU path)")
     emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_s / args.steps,
@@ -182,15 +184,19 @@ def workload_config(world):
 class LayerPool:
     """Device-resident pool of distinct random quantized copies of one layer."""
 
-    def __init__(self, torch, dev, dt, name, k, n, row_parallel, gen):
+    def __init__(self, torch, dev, dt, name, k, n, row_parallel, gen, act_order=True, min_copies=8):
         self.name, self.k, self.n, self.row_parallel = name, k, n, row_parallel
+        self.act_order = act_order
         wbytes = k * n * BITS // 8
-        self.copies = int(min(64, max(8, -(-POOL_BYTES // wbytes))))
+        self.copies = int(min(64, max(min_copies, -(-POOL_BYTES // wbytes))))
         pf = 32 // BITS
         self.q = [torch.randint(-2**31, 2**31 - 1, (k // 16, n * 16 // pf), dtype=torch.int32,
                                 device=dev, generator=gen) for _ in range(self.copies)]
         self.s = [(torch.rand((k // GROUP, n), device=dev, generator=gen) * 0.018 + 0.002).to(dt)
                   for _ in range(self.copies)]
+        self.g_idx = self.perm = None
+        if not act_order:
+            return
         # act-order: sorted group ids as the GEMM sees them, and the sort permutation
         g = (torch.arange(k, device=dev) // GROUP)[torch.randperm(k, device=dev, generator=gen)]
         order = torch.argsort(g, stable=True)
@@ -225,23 +231,34 @@ def run_ours(args, world, rank, local_rank):
     dt = torch.bfloat16
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     pools = [LayerPool(torch, dev, dt, *layer, gen) for layer in LAYERS]
+    # BASELINE config 4: the Llama-3-70B layers as tensor-parallel shards of this world size
+    # (gate_up column-parallel, down row-parallel with the all-reduce), no act-order
+    pools4 = [] if os.environ.get("BENCH_NO_CONFIG4", "0") == "1" else [
+        LayerPool(torch, dev, dt, "gate_up_70b", 8192, 57344 // world, False, gen, act_order=False,
+                  min_copies=2),
+        LayerPool(torch, dev, dt, "down_70b", 28672 // world, 8192, True, gen, act_order=False,
+                  min_copies=2)]
+    all_shapes = [(p, m) for p in pools for m in MS] + [(p, m) for p in pools4 for m in MS4]
     ws = mu.marlin_make_workspace_new(dev)
     max_scratch = max(lib.b200q_marlin_gemm_preferred_scratch_bytes(m, p.n, p.k, 1)
-                      for p in pools for m in MS)
+                      for p, m in all_shapes)
     scratch = torch.empty(max_scratch, dtype=torch.uint8, device=dev)
     a_dev = {(p.k, m): torch.randn((m, p.k), device=dev, dtype=dt, generator=gen)
-             for p in pools for m in MS}
-    c_dev = {(p.n, m): torch.empty((m, p.n), device=dev, dtype=dt) for p in pools for m in MS}
+             for p, m in all_shapes}
+    c_dev = {(p.n, m): torch.empty((m, p.n), device=dev, dtype=dt) for p, m in all_shapes}
     vp = ctypes.c_void_p
     flags = _lib.FLAG_K_FULL | _lib.FLAG_FP32_REDUCE
     qtype = scalar_types.uint4b8
 
-    def raw_call(p, m, copy):
-        """One GEMM through the C ABI on the current stream, inputs resident in HBM."""
+    def raw_call(p, m, copy, reduce=True):
+        """One GEMM through the C ABI on the current stream, inputs resident in HBM.
+        reduce=False leaves the row-parallel output un-reduced (GEMM-only timing)."""
         a, c = a_dev[(p.k, m)], c_dev[(p.n, m)]
-        fused = (custom_ar is not None and p.row_parallel and m * p.n * 2 <= custom_ar.max_size)
+        fused = (reduce and custom_ar is not None and p.row_parallel
+                 and m * p.n * 2 <= custom_ar.max_size)
         args = (vp(a.data_ptr()), p.k, vp(p.q[copy].data_ptr()), vp(p.s[copy].data_ptr()), None,
-                vp(p.g_idx.data_ptr()), vp(p.perm.data_ptr()), None, vp(c.data_ptr()),
+                vp(p.g_idx.data_ptr()) if p.act_order else None,
+                vp(p.perm.data_ptr()) if p.act_order else None, None, vp(c.data_ptr()),
                 vp(scratch.data_ptr()), max_scratch, vp(ws.data_ptr()), ws.numel(), qtype.id,
                 _lib.BF16, m, p.n, p.k, p.k // GROUP, flags)
         cur = vp(torch.cuda.current_stream().cuda_stream)
@@ -252,19 +269,22 @@ def run_ours(args, world, rank, local_rank):
         else:
             rc = lib.b200q_marlin_gemm(*args, cur)
         _lib.check(rc, "b200q_marlin_gemm")
-        if not fused and dist is not None and p.row_parallel:
+        if reduce and not fused and dist is not None and p.row_parallel:
             dist.all_reduce(c)
+
+    ar_check = run_ar_check(torch, dist, D, lib, dev, custom_ar, ar_link, rank, world) \
+        if world > 1 else None
 
     shapes = [(p, m) for p in pools for m in MS]
     use_graphs = os.environ.get("BENCH_NO_GRAPH", "0") != "1"
     stream = torch.cuda.Stream(device=dev)
 
-    def make_runner(p, m, count, first_copy):
+    def make_runner(p, m, count, first_copy, reduce=True):
         """Callable that issues `count` calls rotating over the pool; a CUDA graph
         when enabled (host launch cost would otherwise exceed the kernel time)."""
         def body():
             for i in range(count):
-                raw_call(p, m, (first_copy + i) % p.copies)
+                raw_call(p, m, (first_copy + i) % p.copies, reduce)
         if not use_graphs or count == 0:
             return body, 0
         before = lib.b200q_kernel_launches()
@@ -325,21 +345,31 @@ def run_ours(args, world, rank, local_rank):
 
     # ---- end to end: torch op, host buffers ------------------------------------------------
     e2e_steps = max(1, min(args.steps, 5))
+    if os.environ.get("BENCH_NO_E2E", "0") == "1":
+        e2e_steps = 0
     a_host = {key: t.cpu().pin_memory() for key, t in a_dev.items()}
     c_host = {key: torch.empty(t.shape, dtype=dt).pin_memory() for key, t in c_dev.items()}
     empty = torch.empty(0, dtype=torch.int32, device=dev)
 
     def e2e_call(p, m, copy):
         a = a_host[(p.k, m)].to(dev, non_blocking=True)
-        out = ops.gptq_marlin_gemm(a, None, p.q[copy], None, p.s[copy], None, empty, p.g_idx, p.perm,
-                                   ws, qtype, m, p.n, p.k, is_k_full=True, use_atomic_add=False,
-                                   use_fp32_reduce=True, is_zp_float=False)
+        gemm = lambda: ops.gptq_marlin_gemm(a, None, p.q[copy], None, p.s[copy], None, empty, p.g_idx,
+                                            p.perm, ws, qtype, m, p.n, p.k, is_k_full=True,
+                                            use_atomic_add=False, use_fp32_reduce=True,
+                                            is_zp_float=False)
         if dist is not None and p.row_parallel:
-            out = D.tensor_model_parallel_all_reduce(out)
+            # what RowParallelLinear does: the GEMM all-reduces its own output where it fits
+            with D.fused_all_reduce_scope() as scope:
+                out = gemm()
+            if not scope.done:
+                out = D.tensor_model_parallel_all_reduce(out)
+        else:
+            out = gemm()
         c_host[(p.n, m)].copy_(out, non_blocking=True)
 
-    for p, m in shapes:
-        e2e_call(p, m, 0)
+    if e2e_steps:
+        for p, m in shapes:
+            e2e_call(p, m, 0)
     sync_all()
     ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in shapes]
@@ -353,9 +383,60 @@ def run_ours(args, world, rank, local_rank):
     if dist is not None:
         dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
     ms2 = ms2.tolist()
+
+    # ---- extra timings outside the headline: config 4, and GEMM-only for row-parallel ------
+    def time_shapes(shape_list, steps, reduce=True):
+        """CUDA-event time per call (ms, max over ranks) of each (pool, M): a graph of `steps`
+        calls after one of 3 warm-up calls, ranks aligned before each."""
+        fns = []
+        for p, m in shape_list:
+            w, _ = make_runner(p, m, 3, 0, reduce)
+            t, n_l = make_runner(p, m, steps, 3, reduce)
+            fns.append((w, t, n_l))
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in shape_list]
+        with torch.cuda.stream(stream):
+            for w, _, _ in fns:
+                w()
+        sync_all()
+        with torch.cuda.stream(stream):
+            for (e0, e1), (_, t, _) in zip(evs, fns):
+                if align is not None:
+                    dist.all_reduce(align)
+                e0.record()
+                t()
+                e1.record()
+        sync_all()
+        out = torch.tensor([e0.elapsed_time(e1) / steps for e0, e1 in evs], dtype=torch.float64,
+                           device=dev)
+        if dist is not None:
+            dist.all_reduce(out, op=dist.ReduceOp.MAX)
+        return out.tolist(), sum(n_l for _, _, n_l in fns)
+
+    extra = {}
+    shapes4 = [(p, m) for p in pools4 for m in MS4]
+    if shapes4:
+        with torch.cuda.stream(stream):
+            for p, m in shapes4:
+                raw_call(p, m, 0)
+        torch.cuda.synchronize()
+        steps4 = max(1, min(args.steps, 5))
+        t4, n4 = time_shapes(shapes4, steps4)
+        launches += n4
+        g4 = None
+        if dist is not None:
+            g4, n4g = time_shapes([(p, m) for p, m in shapes4 if p.row_parallel], steps4, reduce=False)
+            launches += n4g
+        extra["config4"] = (shapes4, t4, g4, steps4)
+    if dist is not None:
+        rp = [(p, m) for p, m in shapes if p.row_parallel]
+        g2, n2g = time_shapes(rp, max(1, min(args.steps, 10)), reduce=False)
+        launches += n2g
+        extra["gemm_only"] = (rp, g2)
     decode = run_decode(world, rank, dev) if os.environ.get("BENCH_NO_DECODE", "0") != "1" else None
     if rank == 0:
-        report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, decode)
+        report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, decode,
+               ar_check=ar_check, extra=extra)
     if dist is not None:
         # CUDA graphs that captured NCCL kernels are still alive: tearing the communicator down
         # under them can block, so leave together and let process exit release everything
@@ -365,6 +446,88 @@ def run_ours(args, world, rank, local_rank):
         os._exit(0)
 
 
+def run_ar_check(torch, dist, D, lib, dev, custom_ar, ar_link, rank, world):
+    """Value check of the peer-memory all-reduce kernels before anything is timed: each is
+    compared, bit for bit, with NCCL's all-reduce of the same un-reduced partials, on
+    integer-valued inputs whose sums are exact in fp16 (the method of the reference's
+    tests/distributed/test_custom_all_reduce.py:60-82).  Cases: the GEMM with the all-reduce
+    in its epilogue (M = 1, 16, 32) and followed by the all-reduce kernel (M = 48), the
+    stand-alone kernel at one-shot and two-shot sizes, and all-reduce + residual add +
+    RMSNorm in one kernel.  A mismatch ends the run with a non-zero exit code."""
+    from vllm_b200 import _custom_ops as ops
+    from vllm_b200 import _lib
+    from vllm_b200 import marlin_utils as mu
+    from vllm_b200.scalar_type import scalar_types
+    if custom_ar is None:
+        return {"cases": 0, "ok": True, "note": "peer-memory all-reduce not active (NCCL only)"}
+    import ctypes
+    vp = ctypes.c_void_p
+    dt = torch.float16
+    gen = torch.Generator(device=dev).manual_seed(4321 + rank)
+    cases, bad = 0, []
+    cur = lambda: vp(torch.cuda.current_stream().cuda_stream)
+    # ---- GEMM + all-reduce: K shard of 256 rows, unit scales, activations in {-1, 0, 1} ----
+    K, N = 256, 4096
+    q = torch.randint(-2**31, 2**31 - 1, (K // 16, N * 2), dtype=torch.int32, device=dev, generator=gen)
+    s_ = torch.ones((K // GROUP, N), dtype=dt, device=dev)
+    ws = mu.marlin_make_workspace_new(dev)
+    nscr = lib.b200q_marlin_gemm_preferred_scratch_bytes(64, N, K, 0)
+    scratch = torch.empty(nscr, dtype=torch.uint8, device=dev)
+    flags = _lib.FLAG_K_FULL | _lib.FLAG_FP32_REDUCE
+    for m in (1, 16, 32, 48):
+        a = torch.randint(-1, 2, (m, K), device=dev, generator=gen).to(dt)
+        part, got = torch.empty((m, N), dtype=dt, device=dev), torch.empty((m, N), dtype=dt, device=dev)
+        args = lambda c: (vp(a.data_ptr()), K, vp(q.data_ptr()), vp(s_.data_ptr()), None, None, None,
+                          None, vp(c.data_ptr()), vp(scratch.data_ptr()), nscr, vp(ws.data_ptr()),
+                          ws.numel(), scalar_types.uint4b8.id, _lib.F16, m, N, K, K // GROUP, flags)
+        _lib.check(lib.b200q_marlin_gemm(*args(part), cur()), "b200q_marlin_gemm")
+        _lib.check(lib.b200q_marlin_gemm_all_reduce(*args(got), *ar_link, cur()),
+                   "b200q_marlin_gemm_all_reduce")
+        dist.all_reduce(part)
+        torch.cuda.synchronize()
+        cases += 1
+        if not torch.equal(got, part):
+            bad.append("gemm_all_reduce m=%d" % m)
+    # ---- stand-alone kernel: one-shot sizes, and 512 KiB (two-shot from four ranks up) ----
+    for shape in ((1, 4096), (16, 4096), (64, 4096), (256, 4096)):
+        x = torch.randint(-8, 9, shape, device=dev, generator=gen).to(dt)
+        want = x.clone()
+        dist.all_reduce(want)
+        got = custom_ar.custom_all_reduce(x)
+        torch.cuda.synchronize()
+        cases += 1
+        if got is None or not torch.equal(got, want):
+            bad.append("all_reduce %dx%d" % shape)
+    # ---- all-reduce + residual add + RMSNorm in one kernel vs NCCL, then the local kernel ----
+    common = torch.Generator(device=dev).manual_seed(99)         # same on every rank
+    for (m, n) in ((1, 4096), (64, 4096)):
+        part = torch.randint(-4, 5, (m, n), device=dev, generator=gen).to(dt)
+        res = torch.randint(-4, 5, (m, n), device=dev, generator=common).to(dt)
+        w = (1 + 0.125 * torch.randint(-2, 3, (n,), device=dev, generator=common)).to(dt)
+        want_x, want_res = part.clone(), res.clone()
+        dist.all_reduce(want_x)
+        ops.fused_add_rms_norm(want_x, want_res, w, 1e-5)
+        got_x, got_res = part.clone(), res.clone()
+        done = custom_ar.all_reduce_add_rms_norm(got_x, got_res, w, 1e-5)
+        torch.cuda.synchronize()
+        cases += 1
+        if not (done and torch.equal(got_x, want_x) and torch.equal(got_res, want_res)):
+            bad.append("all_reduce_add_rms_norm %dx%d" % (m, n))
+    err = lib.b200q_device_error(1)
+    flag = torch.tensor([len(bad) + (1 if err else 0)], dtype=torch.int64, device=dev)
+    dist.all_reduce(flag)
+    if int(flag.item()) != 0:
+        sys.stderr.write("rank %d: all-reduce value check FAILED: %s (device error 0x%x)\n"
+                         % (rank, bad, err))
+        if rank == 0:
+            emit({"metric": METRIC, "ar_check": {"cases": cases, "ok": False, "failed": bad}})
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(3)
+    return {"cases": cases, "ok": True,
+            "what": "bitwise equality with NCCL all-reduce on integer-valued fp16 inputs"}
+
+
 def run_decode(world, rank, dev):
     """Third part of the metric: greedy decode of a Llama-3-8B-shaped model (random weights, GPTQ
     uint4b8 g128) whose projections all run through this library, tensor-parallel over the ranks.
@@ -372,7 +535,7 @@ def run_decode(world, rank, dev):
     import torch
     try:
         from vllm_b200.e2e_llama import LlamaConfig, LlamaDecoder, generate
-        batch, prompt, new = 64, 512, 64
+        batch, prompt, new = 64, 512, 128
         cfg = LlamaConfig()
         model = LlamaDecoder(cfg, max_seq=prompt + new + 2, batch=batch, device=dev, tp_rank=rank,
                              tp_size=world)
@@ -396,9 +559,11 @@ def run_decode(world, rank, dev):
         return {"error": repr(exc)[:300]}
 
 
-def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, decode=None):
+def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, decode=None,
+           ar_check=None, extra=None):
     peaks = load_peaks()
     k_steps = args.steps
+    div = lambda a, b: a / b if b else 0.0          # --only leaves some classes empty
     rows = []
     dec_b = dec_t = ten_f = ten_t = e2e_b = e2e_t = str_b = str_t = 0.0
     for (p, m), t, t2 in zip(shapes, ms, ms2):
@@ -406,7 +571,7 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, 
         us = 1e3 * t / k_steps
         rows.append({"layer": p.name, "k": p.k, "n": p.n, "m": m, "us": round(us, 2),
                      "gbs": round(b / us / 1e3, 1), "tflops": round(f / us / 1e6, 2),
-                     "e2e_us": round(1e3 * t2 / e2e_steps, 2)})
+                     "e2e_us": round(div(1e3 * t2, e2e_steps), 2)})
         if m <= 64:
             dec_b += b * k_steps
             dec_t += t
@@ -418,10 +583,10 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, 
         if m >= 1024:
             ten_f += f * k_steps
             ten_t += t
-    value = world * dec_b / dec_t / 1e6            # GB/s, all ranks
-    tflops = world * ten_f / ten_t / 1e9
+    value = world * div(dec_b, dec_t) / 1e6        # GB/s, all ranks
+    tflops = world * div(ten_f, ten_t) / 1e9
     per_gpu_gbs, per_gpu_tf = value / world, tflops / world
-    stream_gbs = str_b / str_t / 1e6  # per GPU: every rank runs the same shapes
+    stream_gbs = div(str_b, str_t) / 1e6  # per GPU: every rank runs the same shapes
     # DRAM bytes of one launch of the dominant decode kernel from the ncu capture summarised in
     # profiles/gemm_stream_gate_up_m16.txt (gate_up, M = 16: 60.9 MB for 61.6 MB algorithmic)
     traffic = 60.9e6
@@ -443,7 +608,7 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, 
                             "unit": "TFLOP/s", "frac": per_gpu_tf / peaks["bf16_tflops"],
                             "traffic": None, "peak_source": peaks["source"],
                             "scope": "M >= 1024 calls"},
-        "e2e": {"value": world * e2e_b / e2e_t / 1e6, "unit": "GB/s",
+        "e2e": {"value": world * div(e2e_b, e2e_t) / 1e6, "unit": "GB/s",
                 "h2d_bytes_per_step": sum(2 * m * p.k for p, m in shapes),
                 "d2h_bytes_per_step": sum(2 * m * p.n for p, m in shapes),
                 "steps": e2e_steps,
@@ -454,7 +619,36 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, 
         "decode": decode,
         "per_shape": rows,
     }
-    if world == 1:
+    if ar_check is not None:
+        line["ar_check"] = ar_check
+    extra = extra or {}
+    if "gemm_only" in extra:
+        # row-parallel shapes without their all-reduce: what the collective costs at this N
+        rp, g2 = extra["gemm_only"]
+        by_key = {(p.name, m): t for (p, m), t in zip(rp, g2)}
+        for row in rows:
+            if (row["layer"], row["m"]) in by_key:
+                row["us_gemm_only"] = round(1e3 * by_key[(row["layer"], row["m"])], 2)
+    if "config4" in extra:
+        shapes4, t4, g4, steps4 = extra["config4"]
+        rows4, gi = [], 0
+        for (p, m), t in zip(shapes4, t4):
+            b, f = algorithmic_bytes(m, p.n, p.k, act_order=False), 2.0 * m * p.n * p.k
+            us = 1e3 * t
+            row = {"layer": p.name, "k": p.k, "n": p.n, "m": m, "us": round(us, 2),
+                   "gbs": round(b / us / 1e3, 1), "tflops": round(f / us / 1e6, 2),
+                   "frac_hbm": round(b / us / 1e3 / peaks["hbm_gbs"], 3),
+                   "frac_tensor": round(f / us / 1e6 / peaks["bf16_tflops"], 3)}
+            if g4 is not None and p.row_parallel:
+                row["us_gemm_only"] = round(1e3 * g4[gi], 2)
+                gi += 1
+            rows4.append(row)
+        line["config4"] = {
+            "workload": "llama3_70b_gptq_uint4b8_g128 tensor-parallel shards at tp=%d: gate_up "
+                        "8192->57344/tp (column-parallel), down 28672/tp->8192 (row-parallel + "
+                        "all-reduce)" % world,
+            "m_values": MS4, "steps": steps4, "per_shape": rows4}
+    if world == 1 and e2e_steps:
         b, s = cpu_sample(LAYERS, 16)
         line["cpu_baseline"] = {
             "value": b / s / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
@@ -483,7 +677,20 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default=None, metavar="LAYER:M",
+                    help="profiling aid: time one (layer, M) of the sweep alone, e.g. gate_up:16, "
+                         "as plain launches (no CUDA graph, no end-to-end / decode / config-4 / "
+                         "CPU parts); the line it prints is not a benchmark result")
     args = ap.parse_args()
+    if args.only:
+        name, m = args.only.split(":")
+        global LAYERS, MS
+        LAYERS = [layer for layer in LAYERS if layer[0] == name]
+        MS = [int(m)]
+        if not LAYERS:
+            raise SystemExit("--only: unknown layer %r" % name)
+        for key in ("BENCH_NO_GRAPH", "BENCH_NO_DECODE", "BENCH_NO_CONFIG4", "BENCH_NO_E2E"):
+            os.environ[key] = "1"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

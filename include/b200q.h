@@ -164,6 +164,14 @@ int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q_weight,
  */
 size_t b200q_all_reduce_state_bytes(void);
 size_t b200q_all_reduce_buffer_bytes(int world, int64_t max_message_bytes);
+/*
+ * How many times a thread polls its own receive buffer for a peer's packets before it
+ * gives up, records 0x1ff in the device error word (b200q_device_error returns 0x101ff)
+ * and skips its output; applies to the calls made after it, process-wide.  0 restores the
+ * default (2^21 polls, about a second).  The reference's kernels wait without a bound
+ * (csrc/custom_all_reduce.cuh:180-262); a bound keeps a lost peer from hanging the GPU.
+ */
+void b200q_all_reduce_set_poll_limit(uint32_t polls);
 int b200q_all_reduce(void* const* peer_bufs, uint32_t* state, int rank, int world,
                      int64_t max_message_bytes, const void* in, void* out, int64_t n_elems,
                      int dtype, b200q_stream_t stream);
@@ -235,6 +243,11 @@ int b200q_silu_and_mul(void* out, const void* input, int64_t num_tokens, int64_t
  *     rejected with B200Q_ESCRATCH (use b200q_marlin_gemm with your own scratch).
  *   - The first call on each device resolves the array's device address
  *     (cudaGetSymbolAddress); make that first call before any stream capture.
+ *     The address stays valid for the life of the device's primary context
+ *     (reload the library after cudaDeviceReset).
+ *   - The array of the CURRENT device is used: the device that owns the tensors
+ *     and the stream must be current (a mismatch is rejected with B200Q_EINVAL
+ *     where the output pointer shows it).
  *   - All calls on a device share the one array: calls that can overlap on the
  *     GPU (different streams) race on it and must be ordered by the caller.
  * This entry point has no counterpart in the reference.

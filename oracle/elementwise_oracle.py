@@ -2,13 +2,18 @@
 
 Test infrastructure only: imported by tests/ and by nothing that ships.
 
-Parity UNPINNED: these follow the rounding points of the reference's CUDA kernels
-as read from their source (csrc/layernorm_kernels.cu:17-58,60-149,
-csrc/activation_kernels.cu:22-38); the kernels cannot run in this environment and
-the reference's pure-torch fall-backs round at different points (variance from the
-unrounded sum, layernorm.py forward_native), so no golden vector of the reference
-backs them.  The tolerances in the tests are those of the reference's own kernel
-tests (atol = rtol = 1e-2, tests/kernels/core/test_layernorm.py).
+Parity pinned on the reference's torch implementations: `rms_norm_native` and
+`silu_and_mul_native` restate RMSNorm.forward_static
+(vllm/model_executor/layers/layernorm.py:180-224) and SiluAndMul.forward_native
+(vllm/model_executor/layers/activation.py:84-87) and are checked bit for bit against
+outputs recorded from them (tests/golden/elementwise_*.npz, made by
+tests/golden/make_golden.py).  `rms_norm`, `fused_add_rms_norm` and `silu_and_mul`
+follow the rounding points of the reference's CUDA kernels as read from their source
+(csrc/layernorm_kernels.cu:17-58,60-149, csrc/activation_kernels.cu:22-38: the sum is
+rounded to 16 bits before the variance is taken, where the torch path takes it from the
+unrounded sum); those kernels cannot run in this environment, so these three are held to
+the recorded torch outputs at the tolerance the reference uses between its kernels and
+its torch path (atol = rtol = 1e-2, tests/kernels/core/test_layernorm.py).
 """
 from __future__ import annotations
 
@@ -41,6 +46,32 @@ def silu_and_mul(x: np.ndarray, dtype: str) -> np.ndarray:
     d = x.shape[-1] // 2
     a, b = x[..., :d].astype(np.float32), x[..., d:].astype(np.float32)
     s = round_to_dtype(a / (1.0 + np.exp(-a, dtype=np.float32)), dtype)
+    return round_to_dtype(s * b, dtype)
+
+
+def rms_norm_native(x: np.ndarray, weight: np.ndarray, eps: float, dtype: str,
+                    residual: np.ndarray | None = None):
+    """RMSNorm.forward_static (layernorm.py:180-224): fp32 sum with the residual, new residual
+    = the sum rounded to 16 bits, variance from the UNROUNDED fp32 sum, x * rsqrt(var + eps) in
+    fp32 rounded to 16 bits, then the product with the weight rounded again.  Returns the
+    output, or (output, new residual) when a residual is given."""
+    x32 = x.astype(np.float32)
+    new_res = None
+    if residual is not None:
+        x32 = x32 + residual.astype(np.float32)
+        new_res = round_to_dtype(x32, dtype)
+    var = np.mean(x32 * x32, axis=-1, keepdims=True, dtype=np.float32)
+    y = round_to_dtype(x32 * (np.float32(1.0) / np.sqrt(var + np.float32(eps))), dtype)
+    out = round_to_dtype(y * weight.astype(np.float32), dtype)
+    return out if residual is None else (out, new_res)
+
+
+def silu_and_mul_native(x: np.ndarray, dtype: str) -> np.ndarray:
+    """SiluAndMul.forward_native (activation.py:84-87): F.silu on the 16-bit first half
+    (computed in fp32, rounded to 16 bits), times the second half, rounded."""
+    d = x.shape[-1] // 2
+    a, b = x[..., :d].astype(np.float32), x[..., d:].astype(np.float32)
+    s = round_to_dtype(a / (np.float32(1.0) + np.exp(-a)), dtype)
     return round_to_dtype(s * b, dtype)
 
 

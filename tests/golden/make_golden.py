@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory from the reference's own
 Python packers (CPU only).
 
-Usage:  python tests/golden/make_golden.py <path-to-reference-checkout> [hqq|fp8]
-        (with `hqq` / `fp8` only that fixture is rewritten)
+Usage:  python tests/golden/make_golden.py <path-to-reference-checkout> [hqq|fp8|elementwise]
+        (with `hqq` / `fp8` / `elementwise` only that fixture is rewritten)
 
 The reference checkout is only needed to (re)generate the fixtures; the tests
 read the committed ``*.npz`` files and never import the reference.  All inputs
@@ -29,6 +29,12 @@ inputs):
                      (marlin_utils_fp8.py:321-352) with the CUDA repack op replaced by the CPU
                      marlin_weights: codes, scales, weight_ref, packed words, Marlin words,
                      permuted scales with the exponent bias fused in, and the product
+  elementwise_{bf16,f16}.npz
+                     the reference's torch implementations of the steps next to the
+                     row-parallel GEMM: RMSNorm.forward_static with and without a residual
+                     (vllm/model_executor/layers/layernorm.py:180-224) and
+                     SiluAndMul.forward_native (vllm/model_executor/layers/activation.py:84-87),
+                     inputs and outputs as 16-bit patterns
 """
 
 import os
@@ -100,6 +106,27 @@ def make_fp8(here, mu, mt) -> None:
             out_ref=(a.float() @ weight_ref.T.float()).numpy())
 
 
+def make_elementwise(here) -> None:
+    import torch
+    from vllm.model_executor.layers.activation import SiluAndMul
+    from vllm.model_executor.layers.layernorm import RMSNorm
+    for tag, dt in (("bf16", torch.bfloat16), ("f16", torch.float16)):
+        torch.manual_seed(11)
+        tokens, hidden, eps = 7, 512, 1e-5
+        x = torch.randn((tokens, hidden), dtype=torch.float32).to(dt)
+        res = torch.randn((tokens, hidden), dtype=torch.float32).to(dt)
+        w = (1 + 0.1 * torch.randn(hidden, dtype=torch.float32)).to(dt)
+        plain = RMSNorm.forward_static(x, eps, hidden, dt, w, None)
+        fused, new_res = RMSNorm.forward_static(x, eps, hidden, dt, w, res)
+        gate_up = (3 * torch.randn((tokens, 2 * hidden), dtype=torch.float32)).to(dt)
+        act = SiluAndMul.forward_native(gate_up)
+        np.savez_compressed(
+            os.path.join(here, f"elementwise_{tag}.npz"), eps=np.float64(eps),
+            x_bits=_bits16(x), res_bits=_bits16(res), w_bits=_bits16(w),
+            rms_bits=_bits16(plain), fused_bits=_bits16(fused), new_res_bits=_bits16(new_res),
+            gate_up_bits=_bits16(gate_up), act_bits=_bits16(act))
+
+
 def main(ref_root: str, only: str | None = None) -> None:
     sys.path.insert(0, ref_root)
     import torch
@@ -116,6 +143,10 @@ def main(ref_root: str, only: str | None = None) -> None:
     if only == "fp8":
         make_fp8(here, mu, mt)
         print("fp8 fixtures written to", here)
+        return
+    if only == "elementwise":
+        make_elementwise(here)
+        print("elementwise fixtures written to", here)
         return
     types = {"uint4b8": scalar_types.uint4b8, "uint4": scalar_types.uint4,
              "uint8b128": scalar_types.uint8b128, "uint8": scalar_types.uint8}
@@ -205,6 +236,7 @@ def main(ref_root: str, only: str | None = None) -> None:
         np.savez_compressed(os.path.join(here, f"gemm_{name}.npz"), **rec)
     make_hqq(here, mu, mt, qu)
     make_fp8(here, mu, mt)
+    make_elementwise(here)
     print("golden fixtures written to", here)
 
 

@@ -22,6 +22,7 @@ def _worker(rank, world, port, q):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"   # also on the exception path below
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -118,12 +119,16 @@ def _worker(rank, world, port, q):
         torch.cuda.synchronize()
         ok &= bool(torch.equal(got_x, want_x)) and bool(torch.equal(got_res, want_res))
     ok &= lib.b200q_device_error(1) == 0
-    q.put((rank, bool(ok)))
-    q.close()
-    q.join_thread()          # the feeder thread must flush before os._exit below
-    dist.barrier()
+    # leave in order: nothing in flight, graphs that hold link kernels gone, the peer buffers
+    # released on every rank, then the process group, then a normal return
     torch.cuda.synchronize()
-    os._exit(0)
+    dist.barrier()
+    del g, g2, layer
+    D.destroy_model_parallel()
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    q.put((rank, bool(ok)))
 
 
 def _worker_guarded(rank, world, port, q):
@@ -149,8 +154,7 @@ def test_custom_all_reduce_matches_nccl(twoshot, monkeypatch):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least two GPUs")
     if twoshot:                      # read by the library in the child processes
-        monkeypatch.setenv("B200Q_AR_TWOSHOT_MIN", "0")
-        monkeypatch.setenv("B200Q_AR_TWOSHOT_WORLD", "2")
+        monkeypatch.setenv("B200Q_DEBUG", "twoshot_any")
     world = min(4, torch.cuda.device_count()) if twoshot else 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

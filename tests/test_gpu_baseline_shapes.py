@@ -94,3 +94,61 @@ def test_full_size_layer_consistency(env, case):
         part = f(a[:m].contiguous()).float()
         assert (part - full[:m]).abs().max().item() <= 2e-2 * scale, (name, m)
     assert int(ws.abs().sum().item()) == 0
+
+
+# Config 2: the benchmarked sweep itself.  Llama-3-8B layers, uint4b8, group 128, act-order
+# (desc_act): the op receives the sorted g_idx and the sort permutation, exactly what the bench
+# passes, so this is the path whose time is reported (activation gather + grouped kernel, every
+# kernel family over M), plus the partial-K form of the same layer (is_k_full = False: groups
+# looked up through g_idx), as tests/kernels/quantization/test_marlin_gemm.py:212-361 crosses
+# act_order with is_k_full.
+CONFIG2 = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672), ("down", 14336, 4096)]
+CONFIG2_MS = (1, 16, 64, 256, 4096)
+
+
+@pytest.mark.parametrize("layer", CONFIG2, ids=lambda c: c[0])
+def test_config2_act_order_full_size(env, layer):
+    torch, G, ops, mu, lib = env
+    from vllm_b200.scalar_type import scalar_types
+    name, K, N = layer
+    group, dtype, tdt = 128, "bfloat16", torch.bfloat16
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    q, s, _ = _random_layer(torch, K, N, 4, K // group, False, tdt, gen)
+    g = (torch.arange(K, device="cuda") // group)[torch.randperm(K, device="cuda", generator=gen)]
+    order = torch.argsort(g, stable=True)
+    g_idx, perm = g[order].to(torch.int32).contiguous(), order.to(torch.int32).contiguous()
+    ws = mu.marlin_make_workspace_new(torch.device("cuda"))
+    e = torch.empty(0, dtype=torch.int32, device="cuda")
+
+    def f(x, k_full=True):
+        return ops.gptq_marlin_gemm(x, None, q, None, s, None, e, g_idx, perm, ws,
+                                    scalar_types.uint4b8, x.shape[0], N, K, k_full, False, True,
+                                    False)
+
+    m_max = max(CONFIG2_MS)
+    a = torch.randn((m_max, K), device="cuda", dtype=tdt, generator=gen)
+    full = f(a).float()
+    torch.cuda.synchronize()
+    assert lib.b200q_device_error(1) == 0
+    scale = full.abs().max().item()
+    # oracle corner: the kernel multiplies the gathered columns a[:, perm] with the rows in
+    # sorted order, whose groups are then contiguous
+    rows = 48
+    a_sorted = G.n16(a[:rows][:, order])
+    ref = _corner_ref(a_sorted, q, s, None, K, 4, group, False, dtype, 8)
+    mf, mr = H.gemm_errors(full[:rows, :64].cpu().numpy(), ref)
+    assert mf <= H.MAX_ABS_FRAC and mr <= H.MEAN_REL, (name, mf, mr)
+    for m in CONFIG2_MS:
+        part = f(a[:m].contiguous()).float()
+        torch.cuda.synchronize()
+        assert (part - full[:m]).abs().max().item() <= 2e-2 * scale, (name, m)
+        if m <= rows:
+            mf, mr = H.gemm_errors(part[:, :64].cpu().numpy(), ref[:m])
+            assert mf <= H.MAX_ABS_FRAC and mr <= 2 * H.MEAN_REL, (name, m, mf, mr)
+    # partial-K form (group looked up per row): same numbers, other kernel
+    for m in (1, 16, 64):
+        part = f(a[:m].contiguous(), k_full=False).float()
+        torch.cuda.synchronize()
+        assert (part - full[:m]).abs().max().item() <= 2e-2 * scale, (name, m, "lookup")
+    assert lib.b200q_device_error(1) == 0
+    assert int(ws.abs().sum().item()) == 0

@@ -28,6 +28,7 @@ EXPORTS = (
     "b200q_marlin_gemm_noalloc",
     "b200q_all_reduce_state_bytes",
     "b200q_all_reduce_buffer_bytes",
+    "b200q_all_reduce_set_poll_limit",
     "b200q_all_reduce",
     "b200q_marlin_gemm_all_reduce",
     "b200q_fused_add_rms_norm",
@@ -100,6 +101,8 @@ def load() -> ctypes.CDLL:
                                                         i64, i64, i32, vp]
     lib.b200q_silu_and_mul.restype = i32
     lib.b200q_silu_and_mul.argtypes = [vp, vp, i64, i64, i32, vp]
+    lib.b200q_all_reduce_set_poll_limit.restype = None
+    lib.b200q_all_reduce_set_poll_limit.argtypes = [c.c_uint32]
     lib.b200q_all_reduce_buffer_bytes.restype = c.c_size_t
     lib.b200q_all_reduce_buffer_bytes.argtypes = [i32, i64]
     lib.b200q_all_reduce.argtypes = [vp, vp, i32, i32, i64, vp, vp, i64, i32, vp]

@@ -7,6 +7,8 @@
 // unbounded waits).
 #include <cstdlib>
 
+#include <atomic>
+
 #include "ar_link.cuh"
 #include "common.cuh"
 
@@ -216,16 +218,10 @@ int launch_all_reduce(const ArLink& link, const void* in, void* out, int64_t n_e
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
-  // two-shot from 256 KiB on four or more ranks (B200Q_AR_TWOSHOT_MIN overrides the size in bytes)
-  static const long long twoshot_min = [] {
-    const char* e = getenv("B200Q_AR_TWOSHOT_MIN");
-    return e ? atoll(e) : 256ll * 1024;
-  }();
-  static const int twoshot_world = [] {
-    const char* e = getenv("B200Q_AR_TWOSHOT_WORLD");  // smallest group that uses it (tests: 2)
-    return e ? atoi(e) : 4;
-  }();
-  const bool twoshot = link.world >= twoshot_world && n_elems * 2 >= twoshot_min;
+  // two-shot from 256 KiB on four or more ranks; B200Q_DEBUG=twoshot_any selects it for every
+  // message and group size (how the two-rank tests reach it)
+  static const bool twoshot_any = debug_flag("twoshot_any");
+  const bool twoshot = twoshot_any || (link.world >= 4 && n_elems * 2 >= 256ll * 1024);
   if (dtype == B200Q_F16)
     B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, twoshot ? ar::allreduce_twoshot_kernel<half>
                                                    : ar::allreduce_oneshot_kernel<half>, p));
@@ -235,6 +231,9 @@ int launch_all_reduce(const ArLink& link, const void* in, void* out, int64_t n_e
   note_launch();
   return B200Q_OK;
 }
+
+// polls before a wait on peer packets gives up (b200q_all_reduce_set_poll_limit)
+static std::atomic<uint32_t> g_poll_limit{kArSpinLimit};
 
 int check_link(void* const* peer_bufs, uint32_t* state, int rank,
                int world, int64_t max_message_bytes, ArLink* link) {
@@ -258,9 +257,14 @@ int check_link(void* const* peer_bufs, uint32_t* state, int rank,
   link->slot_bytes = 2 * max_message_bytes;
   link->rank = rank;
   link->world = world;
+  link->spin_limit = g_poll_limit.load(std::memory_order_relaxed);
   return B200Q_OK;
 }
 }  // namespace b200q
+
+extern "C" void b200q_all_reduce_set_poll_limit(uint32_t polls) {
+  g_poll_limit.store(polls == 0 ? kArSpinLimit : polls, std::memory_order_relaxed);
+}
 
 extern "C" int b200q_all_reduce(void* const* peer_bufs, uint32_t* state, int rank, int world,
                                 int64_t max_message_bytes,

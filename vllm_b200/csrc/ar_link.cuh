@@ -27,7 +27,7 @@
 namespace b200q {
 
 constexpr int kArMaxWorld = 8;
-constexpr uint32_t kArSpinLimit = 1u << 21;  // polls of local memory: a second or so
+constexpr uint32_t kArSpinLimit = 1u << 21;  // default poll limit: a second or so of local polls
 
 struct ArLink {
   void* const* bufs;         // device array [world]: every rank's receive buffer
@@ -35,6 +35,7 @@ struct ArLink {
   int* error;                // local: 0 = ok, 0x1ff after a poll of the peers' packets timed out
   long long slot_bytes;      // packet bytes of one (parity, rank) slot = 2 x the largest message
   int rank, world;           // world == 0: link not in use
+  uint32_t spin_limit;       // polls of local memory before a wait gives up
 };
 
 __device__ __forceinline__ uint32_t ar_ld_volatile(const uint32_t* p) {
@@ -64,7 +65,7 @@ template <int P>
 __device__ __forceinline__ bool ar_collect(const ArLink& l, const char* mybuf, size_t off,
                                            uint32_t flag, uint32_t (&d)[kArMaxWorld][P]) {
   static_assert(P == 1 || P == 2 || P == 4, "packets per element");
-  for (uint32_t spin = 0; spin < kArSpinLimit; ++spin) {
+  for (uint32_t spin = 0; spin < l.spin_limit; ++spin) {
     bool all = true;
 #pragma unroll
     for (int r = 0; r < kArMaxWorld; ++r) {
@@ -99,7 +100,7 @@ __device__ __forceinline__ bool ar_collect(const ArLink& l, const char* mybuf, s
 // Four adjacent packets (32 bytes) of one peer.
 __device__ __forceinline__ bool ar_get4(const ArLink& l, const char* src, uint32_t flag, uint32_t& w0,
                                         uint32_t& w1, uint32_t& w2, uint32_t& w3) {
-  for (uint32_t spin = 0; spin < kArSpinLimit; ++spin) {
+  for (uint32_t spin = 0; spin < l.spin_limit; ++spin) {
     uint32_t f0, f1, f2, f3;
     asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];\n"
                  : "=r"(w0), "=r"(f0), "=r"(w1), "=r"(f1)

@@ -1,6 +1,8 @@
 // extern "C" surface of libb200q: argument validation (mirroring the checks of
 // the reference op, csrc/quantization/gptq_marlin/gptq_marlin.cu:688-902), kernel
 // selection and scratch accounting.  No torch types cross this boundary.
+#include <cuda.h>
+
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -34,13 +36,46 @@ static void query_device(int dev) {
     g_smem_optin[dev & 63] = v;
 }
 
-bool pdl_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("B200Q_NO_PDL");
-    v = (e && e[0] == '1') ? 0 : 1;
+// The one debugging variable of the library: B200Q_DEBUG is a comma-separated list of
+//   no_pdl       launch without programmatic dependent launch
+//   no_tc        route every M through the decode kernels
+//   no_fused_ar  always run the stand-alone all-reduce kernel after the GEMM
+// read once per process.
+bool debug_flag(const char* name) {
+  static const char* env = [] {
+    const char* e = getenv("B200Q_DEBUG");
+    return e ? e : "";
+  }();
+  const size_t n = strlen(name);
+  for (const char* p = env; (p = strstr(p, name)) != nullptr; p += n) {
+    const bool starts = p == env || p[-1] == ',';
+    const bool ends = p[n] == '\0' || p[n] == ',';
+    if (starts && ends) return true;
   }
-  return v == 1;
+  return false;
+}
+
+bool pdl_enabled() {
+  static const bool on = !debug_flag("no_pdl");
+  return on;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn stream_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      return reinterpret_cast<EncodeTiledFn>(ptr);
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();
+  return fn;
 }
 
 int device_sm_count() {
@@ -70,6 +105,29 @@ int64_t tc_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k);
 int tc_error_flag(bool reset);
 int ar_error_flag(bool reset);
 
+// error word of the streaming decode kernel (id of the first bounded wait that ran out)
+__device__ int g_stream_error;
+int* stream_error_ptr() {
+  static int* ptr[64] = {};  // per device; benign race: every caller stores the same address
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (ptr[dev & 63] == nullptr) {
+    void* v = nullptr;
+    if (cudaGetSymbolAddress(&v, g_stream_error) != cudaSuccess) return nullptr;
+    ptr[dev & 63] = static_cast<int*>(v);
+  }
+  return ptr[dev & 63];
+}
+static int stream_error_flag(bool reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_stream_error, sizeof(int)) != cudaSuccess) return -1;
+  if (reset && v != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int));
+  }
+  return v;
+}
+
 int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* out, int64_t size_m,
                         int64_t size_k, cudaStream_t stream);
 
@@ -79,25 +137,9 @@ constexpr int kMaxRowsPerLaunch = 64;
 // upper bound of CTAs any streaming variant launches (2 per SM, <= 256 SMs)
 constexpr int64_t kMaxGrid = 512;
 
-// B200Q_STREAM_NTW=1|2 overrides the slice width of the grouped decode kernel
-// at 16 rows or fewer (a tuning knob; both settings give identical results).
-int grouped_ntw() {
-  static int v = 0;
-  if (v == 0) {
-    const char* e = getenv("B200Q_STREAM_NTW");
-    v = (e && e[0] == '1') ? 1 : 2;
-  }
-  return v;
-}
-
-// B200Q_DISABLE_TC=1 routes every M through the decode kernels (debugging aid).
 bool tc_path_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("B200Q_DISABLE_TC");
-    v = (e && e[0] == '1') ? 0 : 1;
-  }
-  return v == 1;
+  static const bool on = !debug_flag("no_tc");
+  return on;
 }
 
 inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
@@ -129,7 +171,8 @@ extern "C" int b200q_sm_count(void) { return device_sm_count(); }
 extern "C" int b200q_device_error(int reset) {
   const int tc = tc_error_flag(reset != 0);
   const int ar = ar_error_flag(reset != 0);
-  return tc != 0 ? tc : (ar != 0 ? (0x10000 | ar) : 0);
+  const int st = stream_error_flag(reset != 0);
+  return tc != 0 ? tc : (ar != 0 ? (0x10000 | ar) : (st != 0 ? (0x20000 | st) : 0));
 }
 
 extern "C" size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
@@ -155,12 +198,8 @@ int check_link(void* const* peer_bufs, uint32_t* state, int rank, int world,
                int64_t max_message_bytes, ArLink* link);
 }  // namespace b200q
 
-// B200Q_NO_FUSED_AR=1: always the stand-alone all-reduce kernel (debugging aid).
 static bool fused_ar_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("B200Q_NO_FUSED_AR");
-    return !(e && e[0] == '1');
-  }();
+  static const bool on = !debug_flag("no_fused_ar");
   return on;
 }
 
@@ -305,12 +344,8 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     const int rows = (int)((size_m - m0) < kMaxRowsPerLaunch ? (size_m - m0) : kMaxRowsPerLaunch);
     // 8-row blocks of A handled per launch: 1, 2, 4 or 8
     int mb = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
-    // slice width in 64-column tiles: two where the accumulators fit in registers
-    int ntw = 1;
-    if (nt % 2 == 0 && !general_only) {
-      if (gm == kChannel && mb <= 4) ntw = 2;
-      if (gm == kGrouped && mb <= 2) ntw = grouped_ntw();
-    }
+    const int ntw = 1;  // reference-order kernels: one tile per slice (the streaming kernel
+                        // picks its own slice width)
     StreamParams p;
     p.a = static_cast<const char*>(a_used) + (size_t)m0 * lda_used * 2;
     p.lda = lda_used;

@@ -43,7 +43,9 @@ constexpr int64_t kTypeU8 = 8ll << 8 | 1ll << 50;
 // bump the process-wide launch counter (b200q_kernel_launches)
 void note_launch(int n = 1);
 
-// false when B200Q_NO_PDL=1 (programmatic dependent launch off: debugging aid)
+// true when the comma-separated debugging variable B200Q_DEBUG names `name`
+bool debug_flag(const char* name);
+// false with B200Q_DEBUG=no_pdl (programmatic dependent launch off)
 bool pdl_enabled();
 
 int device_sm_count();

@@ -773,11 +773,6 @@ static TcPlan plan_tiles(int64_t m, int64_t n, int64_t k, int sms, int64_t scrat
   // microseconds per 64-deep k-step of one tile on one SM
   static const struct { int bm, bn; double step_us; } kCand[4] = {
       {256, 256, 0.74}, {256, 128, 0.52}, {128, 256, 0.58}, {128, 128, 0.42}};
-  static int force_ks = -1;
-  if (force_ks < 0) {
-    const char* e = getenv("B200Q_TC_KSPLIT");  // tuning aid: fixed split, 1 = never split
-    force_ks = e ? atoi(e) : 0;
-  }
   const int kb_total = (int)(k / kBK);
   TcPlan best = {128, 128, 1, 0};
   double best_cost = 1e300;
@@ -786,7 +781,6 @@ static TcPlan plan_tiles(int64_t m, int64_t n, int64_t k, int sms, int64_t scrat
     if (c.bn == 256 && n <= 128) continue;
     const int64_t tiles = ((m + c.bm - 1) / c.bm) * ((n + c.bn - 1) / c.bn);
     for (int ks = 1; ks <= 8; ++ks) {
-      if (force_ks > 0 && ks != force_ks && !(ks == 1 && force_ks > kb_total / 2)) continue;
       const int64_t bytes = ks > 1 ? tiles * ks * c.bm * c.bn * 4 : 0;
       if (ks > 1 && (kb_total / ks < 2 || bytes > scratch_bytes)) break;
       const double waves = (double)((tiles * ks + sms - 1) / sms);
@@ -805,13 +799,7 @@ static TcPlan plan_tiles(int64_t m, int64_t n, int64_t k, int sms, int64_t scrat
 
 // True when the tensor-core kernel can take this problem.
 bool tc_gemm_supported(int64_t size_m, int64_t size_n, int64_t size_k, int gm) {
-  static int min_m = 0;
-  if (min_m == 0) {
-    const char* e = getenv("B200Q_TC_MIN_M");  // tuning aid: smallest M taken by this kernel
-    min_m = e ? atoi(e) : 33;
-    if (min_m < 1) min_m = 33;
-  }
-  const bool rows_ok = size_m >= min_m;
+  const bool rows_ok = size_m >= 33;
   return rows_ok && size_k % tc::kBK == 0 && size_n % 64 == 0 && gm != kLookup &&
          tc::get_encode_fn() != nullptr;  // group_blocks >= 2 is checked by the caller
 }
@@ -837,17 +825,8 @@ int launch_tc_gemm(const void* a, int64_t lda, const uint32_t* b, const void* sc
   p.m = (int)size_m; p.n = (int)size_n; p.k = (int)size_k;
   p.group_blocks = group_blocks; p.channelwise = channelwise;
   const tc::TcPlan plan = tc::plan_tiles(size_m, size_n, size_k, device_sm_count(), scratch_bytes);
-  int bm = plan.bm, bn = plan.bn;
+  const int bm = plan.bm, bn = plan.bn;
   p.ksplit = plan.ksplit;
-  if (const char* e = getenv("B200Q_TC_TILE")) {  // tuning aid: "BMxBN", e.g. 256x256 (no split)
-    int fm = 0, fn = 0;
-    if (sscanf(e, "%dx%d", &fm, &fn) == 2 && (fm == 128 || fm == 256) && (fn == 128 || fn == 256) &&
-        (fm == 128 || size_m > 128)) {
-      bm = fm;
-      bn = fn;
-      p.ksplit = 1;
-    }
-  }
   p.partials = static_cast<float*>(scratch);
   const bool has_zp = zeros != nullptr;
   if (a_dtype == B200Q_F16)

@@ -24,6 +24,10 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 // Device address of the array, per device.  In host code the array's name is
 // only a handle for the runtime, never an address a kernel may use; the
 // address comes from cudaGetSymbolAddress with the right device current.
+// Two host threads making the first call on a device race on this plain store;
+// the race is benign, both store the same address.  An address is valid for the
+// life of the device's primary context: after cudaDeviceReset the library must be
+// reloaded (the cached address would be stale).
 void* g_scratch_addr[64] = {};
 
 }  // namespace
@@ -52,6 +56,13 @@ extern "C" int b200q_marlin_gemm_noalloc(const void* a, int64_t lda, const uint3
     B200Q_REQUIRE(ptr != nullptr, B200Q_ECUDA, "cudaGetSymbolAddress returned a null address");
     g_scratch_addr[dev] = ptr;
   }
+  // The array used is the current device's: the output must live there too (a stream
+  // or tensors of another GPU would run against the wrong device's scratch).
+  cudaPointerAttributes attr;
+  if (c != nullptr && cudaPointerGetAttributes(&attr, c) == cudaSuccess &&
+      attr.type == cudaMemoryTypeDevice)
+    B200Q_REQUIRE(attr.device == dev, B200Q_EINVAL,
+                  "c lives on device %d but device %d is current", attr.device, dev);
   const size_t need =
       b200q_marlin_gemm_scratch_bytes(size_m, size_n, size_k, g_idx != nullptr ? 1 : 0);
   B200Q_REQUIRE(need <= kNoAllocBytes, B200Q_ESCRATCH,

@@ -11,6 +11,7 @@ without peer access, fall back to the NCCL process group in
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -53,9 +54,13 @@ def active_scope() -> FusedReduceScope | None:
 
 
 class CustomAllreduce:
-    # messages above this go to NCCL (the reference caps its one-stage kernel at 256-512 KiB,
-    # csrc/custom_all_reduce.cuh:592-593, and the whole path at 1-2 MiB on compute capability 10.0)
-    def __init__(self, group, device: torch.device, max_size: int = 1 << 19) -> None:
+    # messages above this go to NCCL: 2 MiB, the reference's cap for its own peer-memory path on
+    # compute capability 10.0 (vllm/distributed/device_communicators/all_reduce_utils.py:40-45)
+    def __init__(self, group, device: torch.device, max_size: int = 1 << 21) -> None:
+        # The kernels use plain peer stores only.  Without this setting torch's rendezvous also
+        # binds the buffer to an NVLink multicast object, which nothing here needs and which
+        # must not outlive a rank that exits while its peers still run.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.lib = _lib.load()
         self.group = group
@@ -76,6 +81,13 @@ class CustomAllreduce:
         torch.cuda.synchronize(device)
         dist.barrier(group=group)          # every rank's buffer is zero before anyone sends
         self.disabled = False
+
+    def close(self) -> None:
+        """Drop the symmetric buffer and its handle; the object stays, disabled."""
+        self.disabled = True
+        self.data_hdl = None
+        self.data = None
+        self.state = None
 
     def should_custom_ar(self, inp: torch.Tensor) -> bool:
         if self.disabled or not inp.is_cuda or inp.dtype not in (torch.float16, torch.bfloat16):

@@ -34,7 +34,7 @@ def initialize_model_parallel(tensor_model_parallel_size: int | None = None, gro
                          f"process group has {_TP_SIZE} ranks")
 
 
-def enable_custom_all_reduce(device: torch.device, max_size: int = 1 << 19) -> bool:
+def enable_custom_all_reduce(device: torch.device, max_size: int = 1 << 21) -> bool:
     """Set up the peer-memory all-reduce for small messages (decode).  Collective: call on
     every rank after initialize_model_parallel.  Returns whether it is active."""
     global _CUSTOM_AR
@@ -53,7 +53,11 @@ def fused_all_reduce_scope():
 
 
 def destroy_model_parallel() -> None:
+    """Forget the group and release the peer-memory buffers (call on every rank, with no
+    kernel of this rank still using the link)."""
     global _TP_GROUP, _TP_RANK, _TP_SIZE, _CUSTOM_AR
+    if _CUSTOM_AR is not None:
+        _CUSTOM_AR.close()
     _TP_GROUP, _TP_RANK, _TP_SIZE, _CUSTOM_AR = None, 0, 1, None
 
 

@@ -5,9 +5,12 @@ from __future__ import annotations
 
 import torch
 
-from vllm_b200.kernels.mixed_precision import MPLinearLayerConfig, choose_mp_linear_kernel
-from vllm_b200.marlin_utils import (check_marlin_supported, marlin_repeat_scales_on_all_ranks,
-                                    verify_marlin_supports_shape)
+from vllm_b200 import _custom_ops as ops
+from vllm_b200.marlin_utils import (apply_gptq_marlin_linear, check_marlin_supported,
+                                    marlin_is_k_full, marlin_make_empty_g_idx,
+                                    marlin_make_workspace_new, marlin_permute_bias,
+                                    marlin_permute_scales, marlin_repeat_scales_on_all_ranks,
+                                    marlin_sort_g_idx, verify_marlin_supports_shape)
 from vllm_b200.parameter import ShardedParameter
 from vllm_b200.scalar_type import scalar_types
 
@@ -65,12 +68,6 @@ class GPTQMarlinLinearMethod:
         device = extra_weight_attrs.get("device")
         verify_marlin_supports_shape(output_size_per_partition, input_size_per_partition,
                                      input_size, qc.group_size if qc.group_size != -1 else input_size)
-        cfg = MPLinearLayerConfig(
-            full_weight_shape=(input_size, output_size),
-            partition_weight_shape=(input_size_per_partition, output_size_per_partition),
-            weight_type=qc.quant_type, act_type=params_dtype, group_size=qc.group_size,
-            zero_points=False, has_g_idx=qc.desc_act)
-        kernel_type = choose_mp_linear_kernel(cfg)
         group_size = qc.group_size if qc.group_size != -1 else input_size
         if marlin_repeat_scales_on_all_ranks(qc.desc_act, qc.group_size, is_row_parallel):
             scales_input_dim, scales_size = None, input_size // group_size       # replicated
@@ -93,12 +90,44 @@ class GPTQMarlinLinearMethod:
                         dtype=torch.int32, device=device),
             input_dim=scales_input_dim, output_dim=1, packed_dim=1, packed_factor=qc.pack_factor,
             weight_loader=weight_loader))
-        self.kernel = kernel_type(cfg, w_q_param_name="qweight", w_s_param_name="scales",
-                                  w_zp_param_name="qzeros", w_gidx_param_name="g_idx")
+        # what the load -> repack -> apply steps below need to know about the shard
+        layer.input_size_per_partition = input_size_per_partition
+        layer.output_size_per_partition = output_size_per_partition
+        layer.is_k_full = marlin_is_k_full(qc.desc_act, is_row_parallel)
 
     def process_weights_after_loading(self, layer: torch.nn.Module) -> None:
-        self.kernel.process_weights_after_loading(layer)
+        """Checkpoint layout -> kernel layout, once per layer: sort the act-order groups,
+        repack the codes on the device (rows visited in sorted order), permute scales and
+        bias.  The symmetric types carry no zero-points (qzeros is dropped)."""
+        qc = self.quant_config
+        device = layer.qweight.device
+        k, n = layer.input_size_per_partition, layer.output_size_per_partition
+
+        def replace(name, data):
+            delattr(layer, name)
+            layer.register_parameter(name, torch.nn.Parameter(data, requires_grad=False))
+
+        layer.workspace = marlin_make_workspace_new(device)
+        if qc.desc_act:
+            g_idx, sort_indices = marlin_sort_g_idx(layer.g_idx.data)
+        else:
+            g_idx = sort_indices = marlin_make_empty_g_idx(device)
+        replace("g_idx", g_idx)
+        layer.g_idx_sort_indices = sort_indices
+        replace("qweight", ops.gptq_marlin_repack(layer.qweight.data.contiguous(), perm=sort_indices,
+                                                   size_k=k, size_n=n, num_bits=qc.weight_bits))
+        replace("scales", marlin_permute_scales(layer.scales.data.contiguous(), size_k=k, size_n=n,
+                                                group_size=qc.group_size))
+        replace("qzeros", marlin_make_empty_g_idx(device))
+        if getattr(layer, "bias", None) is not None:
+            layer.bias.data = marlin_permute_bias(layer.bias)
 
     def apply(self, layer: torch.nn.Module, x: torch.Tensor,
               bias: torch.Tensor | None = None) -> torch.Tensor:
-        return self.kernel.apply_weights(layer, x, bias)
+        return apply_gptq_marlin_linear(
+            input=x, weight=layer.qweight, weight_scale=layer.scales, weight_zp=layer.qzeros,
+            g_idx=layer.g_idx, g_idx_sort_indices=layer.g_idx_sort_indices,
+            workspace=layer.workspace, wtype=self.quant_config.quant_type,
+            input_size_per_partition=layer.input_size_per_partition,
+            output_size_per_partition=layer.output_size_per_partition,
+            is_k_full=layer.is_k_full, bias=bias)
