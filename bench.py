@@ -226,7 +226,7 @@ def run_ours(args, world, rank, local_rank):
         D.initialize_model_parallel(world)
         if os.environ.get("BENCH_NCCL_ONLY", "0") != "1" and D.enable_custom_all_reduce(dev):
             custom_ar = D._CUSTOM_AR
-            ar_link = D.fused_all_reduce_scope().link_args()
+            ar_link = custom_ar.link_args()
     lib = _lib.load()
     dt = torch.bfloat16
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -353,18 +353,16 @@ def run_ours(args, world, rank, local_rank):
 
     def e2e_call(p, m, copy):
         a = a_host[(p.k, m)].to(dev, non_blocking=True)
-        gemm = lambda: ops.gptq_marlin_gemm(a, None, p.q[copy], None, p.s[copy], None, empty, p.g_idx,
-                                            p.perm, ws, qtype, m, p.n, p.k, is_k_full=True,
-                                            use_atomic_add=False, use_fp32_reduce=True,
-                                            is_zp_float=False)
-        if dist is not None and p.row_parallel:
-            # what RowParallelLinear does: the GEMM all-reduces its own output where it fits
-            with D.fused_all_reduce_scope() as scope:
-                out = gemm()
-            if not scope.done:
-                out = D.tensor_model_parallel_all_reduce(out)
-        else:
-            out = gemm()
+        # what RowParallelLinear does: the op all-reduces its own output where it fits the link
+        link = None
+        if dist is not None and p.row_parallel and custom_ar is not None \
+                and custom_ar.fits(m, p.n, dt):
+            link = custom_ar
+        out = ops.gptq_marlin_gemm(a, None, p.q[copy], None, p.s[copy], None, empty, p.g_idx, p.perm,
+                                   ws, qtype, m, p.n, p.k, is_k_full=True, use_atomic_add=False,
+                                   use_fp32_reduce=True, is_zp_float=False, reduce_link=link)
+        if dist is not None and p.row_parallel and link is None:
+            out = D.tensor_model_parallel_all_reduce(out)
         c_host[(p.n, m)].copy_(out, non_blocking=True)
 
     if e2e_steps:
@@ -612,8 +610,10 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, 
                 "h2d_bytes_per_step": sum(2 * m * p.k for p, m in shapes),
                 "d2h_bytes_per_step": sum(2 * m * p.n for p, m in shapes),
                 "steps": e2e_steps,
-                "path": "torch op gptq_marlin_gemm; A from pinned host memory, C back to pinned "
-                        "host memory every call; weights resident (the op takes device tensors)"},
+                "path": "torch op gptq_marlin_gemm (C++ registration; gptq_marlin_gemm_all_reduce "
+                        "for row-parallel layers at N > 1); A from pinned host memory, C back to "
+                        "pinned host memory every call; weights resident (the op takes device "
+                        "tensors)"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "decode": decode,

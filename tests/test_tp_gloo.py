@@ -101,8 +101,8 @@ def test_two_rank_sharding_and_all_reduce(act_order):
 
 
 def _worker_forward(rank, world, port, out_q):
-    """RowParallelLinear.forward on CPU (16-bit weights, torch matmul): with no peer link the
-    fused-reduce scope is inert and the layer falls back to the process group; reduce=False
+    """RowParallelLinear.forward on CPU (16-bit weights, torch matmul): with no peer link
+    (reduce_link() is None) the layer falls back to the process group; reduce=False
     returns the partial sum; the bias is added on rank 0 only."""
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -110,10 +110,7 @@ def _worker_forward(rank, world, port, out_q):
     from vllm_b200 import distributed as D
     from vllm_b200.linear import RowParallelLinear
     D.initialize_model_parallel(world)
-    scope = D.fused_all_reduce_scope()
-    with scope:
-        pass
-    ok = scope.car is None and scope.done is False
+    ok = D.reduce_link() is None
     torch.manual_seed(0)
     K, N, M = 64, 32, 3
     w = torch.randn(N, K)

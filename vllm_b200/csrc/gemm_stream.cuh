@@ -168,7 +168,7 @@ namespace sk {
 
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 216 * 1024;
-constexpr uint32_t kSpinLimit = 1u << 22;      // polls, each may suspend up to kSuspendNs
+constexpr uint32_t kSpinLimit = 1u << 20;      // polls, each may suspend up to kSuspendNs: ~1 s
 constexpr uint32_t kSuspendNs = 1000;
 
 // Error word (StreamParams::error, owned by capi.cu): 0 = ok; else the id of the first wait
@@ -185,9 +185,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-// Bounded wait on a phase parity; on time-out records `what` and carries on, so the kernel
-// always terminates (its output is then invalid and the host sees the error word).
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int what, int* error) {
+// Bounded wait on a phase parity; on time-out records `what`, tells the rest of the CTA
+// through `abort` (shared memory) and carries on; once a CTA has given up none of its
+// waits waits again, so the kernel always terminates promptly (its output is then invalid
+// and the host sees the error word).
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int what, int* error,
+                                          volatile int* abort) {
+  if (*abort != 0) return;
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     uint32_t done;
     asm volatile(
@@ -198,7 +202,9 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int wha
         : "r"(bar), "r"(parity), "r"(kSuspendNs)
         : "memory");
     if (done) return;
+    if ((spin & 1023u) == 1023u && *abort != 0) return;
   }
+  *abort = 1;
   atomicCAS(error, 0, what);
 }
 // packed weights are read once: keep them from displacing A, scales and partials in L2
@@ -264,6 +270,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap a_map, const StreamParams
   constexpr int KPS = C::kKps;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ int s_is_last;
+  __shared__ int s_abort;  // a wait of this CTA timed out: stop waiting
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -284,6 +291,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap a_map, const StreamParams
   const long long u_end = total * (blockIdx.x + 1) / gridDim.x;
 
   if (threadIdx.x == 0) {
+    s_abort = 0;
     for (int s = 0; s < D; ++s) {
       mbar_init(bars + 8 * s, 1);                        // full: the producer's expect_tx arrival
       mbar_init(bars + 8 * (D + s), kConsumerWarps);     // empty: one arrival per consumer warp
@@ -328,7 +336,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap a_map, const StreamParams
           const uint32_t full = bars + 8 * slot;
           const uint32_t base = ring + slot * stage_bytes;
           const bool early = it < D;                      // stage armed in mode 0
-          if (mode == 1 && !early) mbar_wait(bars + 8 * (D + slot), ((it / D) - 1) & 1, 1, p.error);
+          if (mode == 1 && !early) mbar_wait(bars + 8 * (D + slot), ((it / D) - 1) & 1, 1, p.error, &s_abort);
           if (mode == 0 || !early) {
             const unsigned nvalid = __popc(__ballot_sync(0xffffffffu, valid));
             if (lane == 0) mbar_expect_tx(full, nvalid * (run_bytes + C::kABoxBytes));
@@ -348,7 +356,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap a_map, const StreamParams
         // no copy of this CTA may still be in flight when it ends: wait (bounded) for the
         // last stages; in a healthy run the consumers are waiting on the same barriers
         for (int t = it > D ? it - D : 0; t < it; ++t)
-          mbar_wait(bars + 8 * (t % D), (t / D) & 1, 3, p.error);
+          mbar_wait(bars + 8 * (t % D), (t / D) & 1, 3, p.error, &s_abort);
       }
     }
     return;
@@ -481,7 +489,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap a_map, const StreamParams
     for (int st = 0; st < nst; ++st, ++it) {
       const int slot = it % D;
       const uint32_t base = ring + slot * stage_bytes;
-      mbar_wait(bars + 8 * slot, (it / D) & 1, 2, p.error);
+      mbar_wait(bars + 8 * slot, (it / D) & 1, 2, p.error, &s_abort);
 #pragma unroll
       for (int sp = 0; sp < KPS; ++sp) {
         const int step = st * KPS + sp;

@@ -19,40 +19,6 @@ import torch.distributed as dist
 from . import _lib
 
 
-class FusedReduceScope:
-    """While active, the next quantized GEMM issued through ``gptq_marlin_gemm`` all-reduces
-    its own output over the peer link (``b200q_marlin_gemm_all_reduce``) when the output fits
-    a slot; ``done`` tells the caller whether that happened."""
-
-    def __init__(self, car: "CustomAllreduce | None") -> None:
-        self.car = car if (car is not None and not car.disabled) else None
-        self.done = False
-
-    def __enter__(self) -> "FusedReduceScope":
-        global _ACTIVE_SCOPE
-        self._outer, _ACTIVE_SCOPE = _ACTIVE_SCOPE, (self if self.car is not None else None)
-        return self
-
-    def __exit__(self, *exc) -> None:
-        global _ACTIVE_SCOPE
-        _ACTIVE_SCOPE = self._outer
-
-    def accepts(self, c: torch.Tensor) -> bool:
-        return not self.done and self.car.should_custom_ar(c)
-
-    def link_args(self) -> tuple:
-        car, vp = self.car, ctypes.c_void_p
-        return (vp(car.data_hdl.buffer_ptrs_dev), vp(car.state.data_ptr()), car.rank,
-                car.world_size, car.max_size)
-
-
-_ACTIVE_SCOPE: FusedReduceScope | None = None
-
-
-def active_scope() -> FusedReduceScope | None:
-    return _ACTIVE_SCOPE
-
-
 class CustomAllreduce:
     # messages above this go to NCCL: 2 MiB, the reference's cap for its own peer-memory path on
     # compute capability 10.0 (vllm/distributed/device_communicators/all_reduce_utils.py:40-45)
@@ -78,6 +44,9 @@ class CustomAllreduce:
         self.data_hdl = symm_mem.rendezvous(self.data, group.group_name)
         self.state = torch.zeros(self.lib.b200q_all_reduce_state_bytes() // 4, dtype=torch.int32,
                                  device=device)
+        # the ranks' receive buffers as a device tensor, for the torch op that takes the link
+        self.peer_ptrs = torch.tensor(list(self.data_hdl.buffer_ptrs), dtype=torch.int64,
+                                      device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)          # every rank's buffer is zero before anyone sends
         self.disabled = False
@@ -88,6 +57,19 @@ class CustomAllreduce:
         self.data_hdl = None
         self.data = None
         self.state = None
+        self.peer_ptrs = None
+
+    def fits(self, rows: int, cols: int, dtype: torch.dtype) -> bool:
+        """Whether a [rows, cols] output of this dtype can be all-reduced over the link."""
+        nbytes = rows * cols * 2
+        return (not self.disabled and dtype in (torch.float16, torch.bfloat16)
+                and nbytes % 16 == 0 and 0 < nbytes <= self.max_size)
+
+    def link_args(self) -> tuple:
+        """The link as the C ABI takes it (peer_bufs, state, rank, world, max_message_bytes)."""
+        vp = ctypes.c_void_p
+        return (vp(self.peer_ptrs.data_ptr()), vp(self.state.data_ptr()), self.rank,
+                self.world_size, self.max_size)
 
     def should_custom_ar(self, inp: torch.Tensor) -> bool:
         if self.disabled or not inp.is_cuda or inp.dtype not in (torch.float16, torch.bfloat16):
@@ -104,7 +86,7 @@ class CustomAllreduce:
         out = torch.empty_like(inp)
         vp = ctypes.c_void_p
         rc = self.lib.b200q_all_reduce(
-            vp(self.data_hdl.buffer_ptrs_dev), vp(self.state.data_ptr()), self.rank,
+            vp(self.peer_ptrs.data_ptr()), vp(self.state.data_ptr()), self.rank,
             self.world_size, self.max_size,
             vp(inp.data_ptr()), vp(out.data_ptr()), inp.numel(),
             _lib.BF16 if inp.dtype == torch.bfloat16 else _lib.F16,
@@ -122,7 +104,7 @@ class CustomAllreduce:
         n = inp.size(-1)
         vp = ctypes.c_void_p
         rc = self.lib.b200q_all_reduce_fused_add_rms_norm(
-            vp(self.data_hdl.buffer_ptrs_dev), vp(self.state.data_ptr()), self.rank,
+            vp(self.peer_ptrs.data_ptr()), vp(self.state.data_ptr()), self.rank,
             self.world_size, self.max_size, vp(inp.data_ptr()),
             vp(residual.data_ptr()) if residual is not None else None, vp(weight.data_ptr()),
             float(epsilon), inp.numel() // n, n,

@@ -45,11 +45,13 @@ def enable_custom_all_reduce(device: torch.device, max_size: int = 1 << 21) -> b
     return not _CUSTOM_AR.disabled
 
 
-def fused_all_reduce_scope():
-    """Context for a row-parallel layer: the quantized GEMM issued inside it all-reduces its own
-    output when the peer link is up and the output fits (see FusedReduceScope)."""
-    from .custom_all_reduce import FusedReduceScope
-    return FusedReduceScope(_CUSTOM_AR)
+def reduce_link():
+    """The peer-memory link of the TP group (a CustomAllreduce), or None when it is not up.
+    A row-parallel layer hands it to the quantized GEMM op that all-reduces its own output
+    (gptq_marlin_gemm_all_reduce) where the output fits (link.fits)."""
+    if _CUSTOM_AR is None or _CUSTOM_AR.disabled:
+        return None
+    return _CUSTOM_AR
 
 
 def destroy_model_parallel() -> None:

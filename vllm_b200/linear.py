@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from .distributed import (divide, fused_all_reduce_scope, get_tensor_model_parallel_rank,
+from .distributed import (divide, reduce_link, get_tensor_model_parallel_rank,
                           get_tensor_model_parallel_world_size, tensor_model_parallel_all_gather,
                           tensor_model_parallel_all_reduce)
 from .parameter import ShardedParameter
@@ -174,7 +174,11 @@ class RowParallelLinear(LinearBase):
             return self.quant_method.apply(self, input_, bias)
         if all_reduce is not tensor_model_parallel_all_reduce:
             return all_reduce(self.quant_method.apply(self, input_, bias))
-        # GEMM -> all-reduce is one kernel where the peer link is up and the output is small
-        with fused_all_reduce_scope() as scope:
-            out = self.quant_method.apply(self, input_, bias)
-        return out if scope.done else all_reduce(out)
+        # GEMM -> all-reduce is one op (one kernel at decode sizes) where the peer link is up
+        # and the output fits its slots
+        link = reduce_link()
+        rows = input_.numel() // input_.shape[-1]
+        if (link is not None and getattr(self.quant_method, "supports_reduce_link", False)
+                and link.fits(rows, self.output_size_per_partition, input_.dtype)):
+            return self.quant_method.apply(self, input_, bias, reduce_link=link)
+        return all_reduce(self.quant_method.apply(self, input_, bias))

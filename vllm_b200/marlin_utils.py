@@ -234,7 +234,10 @@ def apply_gptq_marlin_linear(input: torch.Tensor, weight: torch.Tensor,
                              workspace: torch.Tensor, wtype: ScalarType,
                              output_size_per_partition: int, input_size_per_partition: int,
                              is_k_full: bool, bias: torch.Tensor | None = None,
-                             use_fp32_reduce: bool = USE_FP32_REDUCE_DEFAULT) -> torch.Tensor:
+                             use_fp32_reduce: bool = USE_FP32_REDUCE_DEFAULT,
+                             reduce_link=None) -> torch.Tensor:
+    """reduce_link (not in the reference): a peer-memory link; the output is then all-reduced
+    over it by the same op (row-parallel layers)."""
     reshaped_x = input.reshape(-1, input.shape[-1])
     out_shape = input.shape[:-1] + (output_size_per_partition,)
     use_atomic_add = should_use_atomic_add_reduce(
@@ -244,7 +247,8 @@ def apply_gptq_marlin_linear(input: torch.Tensor, weight: torch.Tensor,
         reshaped_x, None, weight, bias, weight_scale, None, weight_zp, g_idx,
         g_idx_sort_indices, workspace, wtype, size_m=reshaped_x.shape[0],
         size_n=output_size_per_partition, size_k=input_size_per_partition, is_k_full=is_k_full,
-        use_atomic_add=use_atomic_add, use_fp32_reduce=use_fp32_reduce, is_zp_float=False)
+        use_atomic_add=use_atomic_add, use_fp32_reduce=use_fp32_reduce, is_zp_float=False,
+        reduce_link=reduce_link)
     return output.reshape(out_shape)
 
 
@@ -254,7 +258,8 @@ def apply_awq_marlin_linear(input: torch.Tensor, weight: torch.Tensor,
                             workspace: torch.Tensor, quant_type: ScalarType,
                             output_size_per_partition: int, input_size_per_partition: int,
                             bias: torch.Tensor | None = None,
-                            use_fp32_reduce: bool = USE_FP32_REDUCE_DEFAULT) -> torch.Tensor:
+                            use_fp32_reduce: bool = USE_FP32_REDUCE_DEFAULT,
+                            reduce_link=None) -> torch.Tensor:
     reshaped_x = input.reshape(-1, input.shape[-1])
     out_shape = input.shape[:-1] + (output_size_per_partition,)
     use_atomic_add = should_use_atomic_add_reduce(
@@ -264,5 +269,6 @@ def apply_awq_marlin_linear(input: torch.Tensor, weight: torch.Tensor,
         reshaped_x, None, weight, bias, weight_scale, None, weight_zp, g_idx,
         g_idx_sort_indices, workspace, quant_type, size_m=reshaped_x.shape[0],
         size_n=output_size_per_partition, size_k=input_size_per_partition,
-        use_atomic_add=use_atomic_add, use_fp32_reduce=use_fp32_reduce, is_zp_float=False)
+        use_atomic_add=use_atomic_add, use_fp32_reduce=use_fp32_reduce, is_zp_float=False,
+        reduce_link=reduce_link)
     return output.reshape(out_shape)

@@ -52,6 +52,8 @@ class AWQMarlinConfig:
 
 
 class AWQMarlinLinearMethod:
+    supports_reduce_link = True   # apply() can all-reduce its output over a peer link
+
     def __init__(self, quant_config: AWQMarlinConfig) -> None:
         self.quant_config = quant_config
 
@@ -105,10 +107,11 @@ class AWQMarlinLinearMethod:
             layer.bias.data = marlin_permute_bias(layer.bias)
 
     def apply(self, layer: torch.nn.Module, x: torch.Tensor,
-              bias: torch.Tensor | None = None) -> torch.Tensor:
+              bias: torch.Tensor | None = None, reduce_link=None) -> torch.Tensor:
         return apply_awq_marlin_linear(
             input=x, weight=layer.qweight, weight_scale=layer.scales, weight_zp=layer.qzeros,
             g_idx=layer.g_idx, g_idx_sort_indices=layer.g_idx_sort_indices,
             workspace=layer.workspace, quant_type=self.quant_config.quant_type,
             output_size_per_partition=layer.output_size_per_partition,
-            input_size_per_partition=layer.input_size_per_partition, bias=bias)
+            input_size_per_partition=layer.input_size_per_partition, bias=bias,
+            reduce_link=reduce_link)

@@ -55,6 +55,8 @@ class GPTQMarlinConfig:
 
 
 class GPTQMarlinLinearMethod:
+    supports_reduce_link = True   # apply() can all-reduce its output over a peer link
+
     def __init__(self, quant_config: GPTQMarlinConfig) -> None:
         self.quant_config = quant_config
 
@@ -123,11 +125,11 @@ class GPTQMarlinLinearMethod:
             layer.bias.data = marlin_permute_bias(layer.bias)
 
     def apply(self, layer: torch.nn.Module, x: torch.Tensor,
-              bias: torch.Tensor | None = None) -> torch.Tensor:
+              bias: torch.Tensor | None = None, reduce_link=None) -> torch.Tensor:
         return apply_gptq_marlin_linear(
             input=x, weight=layer.qweight, weight_scale=layer.scales, weight_zp=layer.qzeros,
             g_idx=layer.g_idx, g_idx_sort_indices=layer.g_idx_sort_indices,
             workspace=layer.workspace, wtype=self.quant_config.quant_type,
             input_size_per_partition=layer.input_size_per_partition,
             output_size_per_partition=layer.output_size_per_partition,
-            is_k_full=layer.is_k_full, bias=bias)
+            is_k_full=layer.is_k_full, bias=bias, reduce_link=reduce_link)
