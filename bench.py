@@ -230,7 +230,9 @@ def run_ours(args, world, rank, local_rank):
     lib = _lib.load()
     dt = torch.bfloat16
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
-    pools = [LayerPool(torch, dev, dt, *layer, gen) for layer in LAYERS]
+    pools = [LayerPool(torch, dev, dt, *layer, gen,
+                       act_order=os.environ.get("BENCH_NO_ACT_ORDER", "0") != "1")
+             for layer in LAYERS]
     # BASELINE config 4: the Llama-3-70B layers as tensor-parallel shards of this world size
     # (gate_up column-parallel, down row-parallel with the all-reduce), no act-order
     pools4 = [] if os.environ.get("BENCH_NO_CONFIG4", "0") == "1" else [
@@ -679,8 +681,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default=None, metavar="LAYER:M",
                     help="profiling aid: time one (layer, M) of the sweep alone, e.g. gate_up:16, "
-                         "as plain launches (no CUDA graph, no end-to-end / decode / config-4 / "
-                         "CPU parts); the line it prints is not a benchmark result")
+                         "without the end-to-end / decode / config-4 / CPU parts; the line it "
+                         "prints is not a benchmark result")
     args = ap.parse_args()
     if args.only:
         name, m = args.only.split(":")
@@ -689,7 +691,7 @@ def main():
         MS = [int(m)]
         if not LAYERS:
             raise SystemExit("--only: unknown layer %r" % name)
-        for key in ("BENCH_NO_GRAPH", "BENCH_NO_DECODE", "BENCH_NO_CONFIG4", "BENCH_NO_E2E"):
+        for key in ("BENCH_NO_DECODE", "BENCH_NO_CONFIG4", "BENCH_NO_E2E"):
             os.environ[key] = "1"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     world = int(os.environ.get("WORLD_SIZE", "1"))

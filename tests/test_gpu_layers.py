@@ -66,7 +66,7 @@ def test_gptq_layers_tp_emulated(env, act_order, dtype, M):
         rl = RowParallelLinear(K, N, tp_rank=r, tp_size=tp, reduce_results=False, **kw)
         _load_gptq(torch, rl, L, ckpt_g_idx)
         if act_order:
-            assert rl.quant_method.kernel.is_k_full is False   # group lookup path
+            assert rl.is_k_full is False   # group lookup path
         total += G.n16(rl(a[:, r * K // tp:(r + 1) * K // tp].contiguous()))
     mf, mr = H.gemm_errors(total, ref)
     assert mf <= H.MAX_ABS_FRAC and mr <= 2 * H.MEAN_REL   # two 16-bit roundings of partial sums

@@ -1,0 +1,77 @@
+"""torch.library.opcheck on the operators registered from C++ (schema, fake kernel and
+autograd registration consistency), as the reference does for each of its ops
+(tests/kernels/utils.py:1300 `opcheck`, used at tests/kernels/quantization/
+test_marlin_gemm.py:141,196,310,419 and tests/kernels/core/test_permute_cols.py)."""
+import pytest
+
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+# what the reference's helper runs by default; the autograd tests do not apply to these
+# inference-only ops
+CHECKS = ("test_schema", "test_autograd_registration", "test_faketensor")
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+
+    from tests import gpu_utils as G
+    from vllm_b200 import _custom_ops as ops
+    from vllm_b200 import marlin_utils as mu
+    return torch, G, ops, mu, getattr(torch.ops, ops.ops_namespace())
+
+
+def test_opcheck_repack_and_permute(env):
+    torch, G, ops, mu, ns = env
+    K, N = 256, 128
+    L = H.make_layer(K, N, "uint4b8", 64, True, "float16")
+    torch.library.opcheck(ns.gptq_marlin_repack,
+                          (G.ti32(L.gptq_qweight), G.ti32(L.sort_idx), K, N, 4), test_utils=CHECKS)
+    torch.library.opcheck(ns.gptq_marlin_repack,
+                          (G.ti32(L.gptq_qweight), G.ti32(None), K, N, 4), test_utils=CHECKS)
+    torch.library.opcheck(ns.awq_marlin_repack, (G.ti32(L.awq_qweight), K, N, 4),
+                          test_utils=CHECKS)
+    a = torch.randn((5, K), dtype=torch.float16, device="cuda")
+    torch.library.opcheck(ns.permute_cols, (a, G.ti32(L.sort_idx)), test_utils=CHECKS)
+
+
+@pytest.mark.parametrize("m", [1, 48, 200])
+def test_opcheck_gemm(env, m):
+    """M = 1 takes the decode kernel, 48 and 200 the tensor-core kernel."""
+    torch, G, ops, mu, ns = env
+    K, N = 512, 256
+    L = H.make_layer(K, N, "uint4b8", 128, True, "bfloat16")
+    a = torch.randn((m, K), dtype=torch.bfloat16, device="cuda")
+    ws = mu.marlin_make_workspace_new(torch.device("cuda"))
+    args = (a, None, G.ti32(L.marlin_q), None, G.t16(L.marlin_s, "bfloat16"), None, G.ti32(None),
+            G.ti32(L.g_idx), G.ti32(L.sort_idx), ws, L.type_id, m, N, K, True, False, True, False)
+    torch.library.opcheck(ns.gptq_marlin_gemm, args, test_utils=CHECKS)
+    assert int(ws.abs().sum().item()) == 0
+
+
+def test_cpp_checks_raise_like_the_reference(env):
+    """The C++ checks turn into RuntimeError with the reference's messages."""
+    torch, G, ops, mu, ns = env
+    K, N = 512, 256
+    L = H.make_layer(K, N, "uint4b8", 128, False, "float16")
+    ws = mu.marlin_make_workspace_new(torch.device("cuda"))
+    e = G.ti32(None)
+    a = torch.randn((4, K), dtype=torch.float16, device="cuda")
+    good = [a, None, G.ti32(L.marlin_q), None, G.t16(L.marlin_s, "float16"), None, e, e, e, ws,
+            L.type_id, 4, N, K, True, False, True, False]
+    bad = list(good)
+    bad[12] = N + 64                                     # size_n does not match the weights
+    with pytest.raises(RuntimeError, match="size_n"):
+        ns.gptq_marlin_gemm(*bad)
+    bad = list(good)
+    bad[0] = a.float()                                   # unsupported activation dtype
+    with pytest.raises(RuntimeError):
+        ns.gptq_marlin_gemm(*bad)
+    bad = list(good)
+    bad[9] = ws[:8]                                      # workspace below the number of SMs
+    with pytest.raises(RuntimeError, match="workspace"):
+        ns.gptq_marlin_gemm(*bad)
+    with pytest.raises(RuntimeError, match="num_bits"):
+        ns.gptq_marlin_repack(G.ti32(L.gptq_qweight), e, K, N, 5)

@@ -1,8 +1,6 @@
 // extern "C" surface of libb200q: argument validation (mirroring the checks of
 // the reference op, csrc/quantization/gptq_marlin/gptq_marlin.cu:688-902), kernel
 // selection and scratch accounting.  No torch types cross this boundary.
-#include <cuda.h>
-
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -60,24 +58,6 @@ bool pdl_enabled() {
   return on;
 }
 
-// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn stream_encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
-            cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      return reinterpret_cast<EncodeTiledFn>(ptr);
-    return static_cast<EncodeTiledFn>(nullptr);
-  }();
-  return fn;
-}
-
 int device_sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
@@ -105,28 +85,6 @@ int64_t tc_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k);
 int tc_error_flag(bool reset);
 int ar_error_flag(bool reset);
 
-// error word of the streaming decode kernel (id of the first bounded wait that ran out)
-__device__ int g_stream_error;
-int* stream_error_ptr() {
-  static int* ptr[64] = {};  // per device; benign race: every caller stores the same address
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-  if (ptr[dev & 63] == nullptr) {
-    void* v = nullptr;
-    if (cudaGetSymbolAddress(&v, g_stream_error) != cudaSuccess) return nullptr;
-    ptr[dev & 63] = static_cast<int*>(v);
-  }
-  return ptr[dev & 63];
-}
-static int stream_error_flag(bool reset) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_stream_error, sizeof(int)) != cudaSuccess) return -1;
-  if (reset && v != 0) {
-    int zero = 0;
-    cudaMemcpyToSymbol(g_stream_error, &zero, sizeof(int));
-  }
-  return v;
-}
 
 int launch_permute_cols(const void* a, int64_t lda, const int32_t* perm, void* out, int64_t size_m,
                         int64_t size_k, cudaStream_t stream);
@@ -171,8 +129,7 @@ extern "C" int b200q_sm_count(void) { return device_sm_count(); }
 extern "C" int b200q_device_error(int reset) {
   const int tc = tc_error_flag(reset != 0);
   const int ar = ar_error_flag(reset != 0);
-  const int st = stream_error_flag(reset != 0);
-  return tc != 0 ? tc : (ar != 0 ? (0x10000 | ar) : (st != 0 ? (0x20000 | st) : 0));
+  return tc != 0 ? tc : (ar != 0 ? (0x10000 | ar) : 0);
 }
 
 extern "C" size_t b200q_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k,
@@ -344,8 +301,12 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     const int rows = (int)((size_m - m0) < kMaxRowsPerLaunch ? (size_m - m0) : kMaxRowsPerLaunch);
     // 8-row blocks of A handled per launch: 1, 2, 4 or 8
     int mb = rows <= 8 ? 1 : rows <= 16 ? 2 : rows <= 32 ? 4 : 8;
-    const int ntw = 1;  // reference-order kernels: one tile per slice (the streaming kernel
-                        // picks its own slice width)
+    // slice width in 64-column tiles: two where the accumulators fit in registers
+    int ntw = 1;
+    if (nt % 2 == 0 && !general_only) {
+      if (gm == kChannel && mb <= 4) ntw = 2;
+      if (gm == kGrouped && mb <= 2) ntw = 2;
+    }
     StreamParams p;
     p.a = static_cast<const char*>(a_used) + (size_t)m0 * lda_used * 2;
     p.lda = lda_used;

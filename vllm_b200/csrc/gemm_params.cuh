@@ -25,10 +25,7 @@ struct StreamParams {
   int32_t* counters;       // zero on entry / exit
   int m, n, k;
   int kt_total;            // K / 16
-  int slices;              // column slices: N / (64 * tiles per slice)
-  int wn;                  // streaming kernel: 64-column tiles per slice (1, 2, 4)
-  int ring_stages;         // streaming kernel: depth of the shared-memory ring
-  int* error;              // streaming kernel: device error word (bounded waits)
+  int slices;              // N / (64 * NTW)
   int group_blocks;        // k-tiles per scale group (kGrouped)
   int num_groups;
   int zp_float;            // zeros holds 16-bit floats [G, N] in the scales' layout

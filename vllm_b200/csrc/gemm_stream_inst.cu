@@ -25,15 +25,31 @@ namespace {
 using T = InstT;
 constexpr int B = INST_BITS;
 
-// `rows8` = 8-row blocks of A (1, 2, 4, 8); up to 4 blocks run the streaming kernel, 8 blocks
-// (64 rows) hold too many accumulators for it and run the reference-order kernel.
-template <bool HAS_ZP, int GM>
-int streamed(const StreamParams& p, int rows8, int max_ctas, cudaStream_t stream) {
-  switch (rows8) {
-    case 1: return launch_stream<T, B, HAS_ZP, GM, 1>(p, max_ctas, stream);
-    case 2: return launch_stream<T, B, HAS_ZP, GM, 2>(p, max_ctas, stream);
-    case 4: return launch_stream<T, B, HAS_ZP, GM, 4>(p, max_ctas, stream);
-    case 8: return launch_lookup<T, B, HAS_ZP, GM, 4, 1>(p, max_ctas, stream);
+// `rows8` = 8-row blocks of A (1, 2, 4, 8); 8 blocks (64 rows) hold too many
+// accumulators for the streaming kernel and run the reference-order kernel.
+template <bool HAS_ZP>
+int channel(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
+  switch (rows8 * 10 + ntw) {
+    case 11: return launch_stream<T, B, HAS_ZP, kChannel, 1, 1>(p, max_ctas, stream);
+    case 12: return launch_stream<T, B, HAS_ZP, kChannel, 1, 2>(p, max_ctas, stream);
+    case 21: return launch_stream<T, B, HAS_ZP, kChannel, 2, 1>(p, max_ctas, stream);
+    case 22: return launch_stream<T, B, HAS_ZP, kChannel, 2, 2>(p, max_ctas, stream);
+    case 41: return launch_stream<T, B, HAS_ZP, kChannel, 4, 1>(p, max_ctas, stream);
+    case 42: return launch_stream<T, B, HAS_ZP, kChannel, 4, 2>(p, max_ctas, stream);
+    case 81: return launch_lookup<T, B, HAS_ZP, kChannel, 4, 1>(p, max_ctas, stream);
+  }
+  return B200Q_EUNSUPPORTED;
+}
+
+template <bool HAS_ZP>
+int grouped(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
+  switch (rows8 * 10 + ntw) {
+    case 11: return launch_stream<T, B, HAS_ZP, kGrouped, 1, 1>(p, max_ctas, stream);
+    case 12: return launch_stream<T, B, HAS_ZP, kGrouped, 1, 2>(p, max_ctas, stream);
+    case 21: return launch_stream<T, B, HAS_ZP, kGrouped, 2, 1>(p, max_ctas, stream);
+    case 22: return launch_stream<T, B, HAS_ZP, kGrouped, 2, 2>(p, max_ctas, stream);
+    case 41: return launch_stream<T, B, HAS_ZP, kGrouped, 4, 1>(p, max_ctas, stream);
+    case 81: return launch_lookup<T, B, HAS_ZP, kGrouped, 4, 1>(p, max_ctas, stream);
   }
   return B200Q_EUNSUPPORTED;
 }
@@ -93,11 +109,11 @@ int dispatch_stream<InstT, INST_BITS>(const StreamParams& p, bool has_zp, int gm
     return (has_zp && gm == kGrouped) ? grouped_zp_float(p, mb, ntw, max_ctas, stream)
                                       : B200Q_EUNSUPPORTED;
   if (gm == kChannel)
-    return has_zp ? streamed<true, kChannel>(p, mb, max_ctas, stream)
-                  : streamed<false, kChannel>(p, mb, max_ctas, stream);
+    return has_zp ? channel<true>(p, mb, ntw, max_ctas, stream)
+                  : channel<false>(p, mb, ntw, max_ctas, stream);
   if (gm == kGrouped)
-    return has_zp ? streamed<true, kGrouped>(p, mb, max_ctas, stream)
-                  : streamed<false, kGrouped>(p, mb, max_ctas, stream);
+    return has_zp ? grouped<true>(p, mb, ntw, max_ctas, stream)
+                  : grouped<false>(p, mb, ntw, max_ctas, stream);
   if (has_zp) return B200Q_EUNSUPPORTED;
   return lookup(p, mb, ntw, max_ctas, stream);
 }

@@ -51,8 +51,8 @@ constexpr int kProducerWarp = kEpiWarp0 + 4;
 constexpr int kMmaWarp = kProducerWarp + 1;
 constexpr int kThreads = 32 * (kMmaWarp + 1);
 constexpr int64_t kMaxSplitBytes = 64ll << 20;  // cap on the fp32 partials of a k-split
-constexpr uint32_t kSpinLimit = 1u << 24;   // polls; each poll may sleep up to kSuspendNs
-constexpr uint32_t kSuspendNs = 1000;       // try_wait suspend-time hint: pollers leave the issue slots alone
+constexpr uint32_t kSpinLimit = 1u << 24;   // polls (try_wait without a suspend-time hint: a waiter
+                                            // given a 1 us hint was seen to sleep the hint out)
 
 // 0 = ok; else (role << 8) | barrier id of the first wait that ever timed out (sticky, for the
 // host to read).  Roles of the same CTA tell each other to stop through a shared-memory flag.
@@ -94,10 +94,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int wha
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(done)
-        : "r"(bar), "r"(parity), "r"(kSuspendNs)
+        : "r"(bar), "r"(parity)
         : "memory");
     if (done) return true;
     if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
