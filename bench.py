@@ -408,18 +408,43 @@ def run_ours(args, world, rank, local_rank):
         for p, m in shapes:
             e2e_call(p, m, 0)
     sync_all()
-    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in shapes]
-    for (e0, e1), (p, m) in zip(ev2, shapes):
-        e0.record()
-        for i in range(e2e_steps):
-            e2e_call(p, m, (1 + i) % p.copies)
-        e1.record()
-    sync_all()
-    ms2 = torch.tensor([e0.elapsed_time(e1) for e0, e1 in ev2], dtype=torch.float64, device=dev)
-    if dist is not None:
-        dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
-    ms2 = ms2.tolist()
+
+    def time_e2e(graphs):
+        """ms per shape for e2e_steps calls of (copy A from pinned host memory, operator, copy C
+        to pinned host memory), max over ranks.  graphs=True: the calls of a shape are captured
+        once in a CUDA graph and replayed (how a serving engine issues decode steps: the host
+        cost of the operator call is paid at capture); False: issued call by call."""
+        runs = []
+        for p, m in shapes:
+            def body(p=p, m=m):
+                for i in range(e2e_steps):
+                    e2e_call(p, m, (1 + i) % p.copies)
+            if graphs and e2e_steps:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    body()
+                runs.append(g.replay)
+            else:
+                runs.append(body)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in shapes]
+        sync_all()
+        with torch.cuda.stream(stream):
+            for (e0, e1), run in zip(evs, runs):
+                if align is not None and graphs:
+                    dist.all_reduce(align)
+                e0.record()
+                run()
+                e1.record()
+        sync_all()
+        out = torch.tensor([e0.elapsed_time(e1) for e0, e1 in evs], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(out, op=dist.ReduceOp.MAX)
+        return out.tolist()
+
+    ms2 = time_e2e(use_graphs)
+    ms2_eager = time_e2e(False)
+    extra["e2e_eager"] = ms2_eager
 
     shapes4 = [(p, m) for p in pools4 for m in MS4]
     if shapes4:
@@ -620,7 +645,8 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, 
                 "path": "torch op gptq_marlin_gemm (C++ registration; gptq_marlin_gemm_all_reduce "
                         "for row-parallel layers at N > 1); A from pinned host memory, C back to "
                         "pinned host memory every call; weights resident (the op takes device "
-                        "tensors)"},
+                        "tensors); the calls of a shape are captured in a CUDA graph (copies "
+                        "included) and replayed; eager_value = the same calls issued one by one"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "decode": decode,
@@ -629,6 +655,14 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, 
     if ar_check is not None:
         line["ar_check"] = ar_check
     extra = extra or {}
+    if "e2e_eager" in extra:
+        eb = et = 0.0
+        for (p, m), t2, row in zip(shapes, extra["e2e_eager"], rows):
+            row["e2e_eager_us"] = round(div(1e3 * t2, e2e_steps), 2)
+            if m <= 64:
+                eb += algorithmic_bytes(m, p.n, p.k) * e2e_steps
+                et += t2
+        line["e2e"]["eager_value"] = world * div(eb, et) / 1e6
     if "gemm_only" in extra:
         # row-parallel shapes without their all-reduce: what the collective costs at this N
         rp, g2 = extra["gemm_only"]
