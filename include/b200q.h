@@ -177,6 +177,30 @@ int b200q_all_reduce(void* const* peer_bufs, uint32_t* state, int rank, int worl
                      int dtype, b200q_stream_t stream);
 
 /*
+ * The same GEMM for float4_e2m1f weights (b_q_type float4_e2m1f of
+ * csrc/quantization/gptq_marlin/gptq_marlin.cu:818-829, 907-917, which the reference
+ * selects by the dtype of b_scales):
+ *   scale_kind B200Q_FP4_SCALES_E4M3  NVFP4: group size 16, b_scales = bytes [K/16, N] as
+ *              nvfp4_marlin_process_scales returns them (float8_e4m3fn-typed tensor),
+ *              global_scale = one 16-bit value as nvfp4_marlin_process_global_scale
+ *              returns it (vllm/model_executor/layers/quantization/utils/marlin_utils_fp4.py:28-90)
+ *   scale_kind B200Q_FP4_SCALES_E8M0  MXFP4: group size 32, b_scales = bytes [K/32, N] as
+ *              mxfp4_marlin_process_scales returns them (float8_e8m0fnu), global_scale
+ *              null, bfloat16 activations only
+ * b_q_weight is the Marlin layout of the 4-bit codes (gptq_marlin_repack with num_bits 4);
+ * no zero-points, no act-order; K / group size must be even.  The other arguments as in
+ * b200q_marlin_gemm.
+ */
+#define B200Q_FP4_SCALES_E4M3 1
+#define B200Q_FP4_SCALES_E8M0 2
+int b200q_marlin_gemm_fp4(const void* a, int64_t lda, const uint32_t* b_q_weight,
+                          const void* b_scales, const void* global_scale, int scale_kind,
+                          const void* b_bias, void* c, void* scratch, size_t scratch_bytes,
+                          int32_t* workspace, int64_t workspace_len, int a_dtype, int64_t size_m,
+                          int64_t size_n, int64_t size_k, int64_t num_groups,
+                          b200q_stream_t stream);
+
+/*
  * b200q_marlin_gemm followed by the SUM all-reduce of C over the same peer link, as
  * RowParallelLinear does (vllm/model_executor/layers/linear.py:1386-1411: the
  * quantized matmul of the K shard, then tensor_model_parallel_all_reduce).  Where one

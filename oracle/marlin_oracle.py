@@ -392,6 +392,90 @@ def dequantize_fp8(codes: np.ndarray, scales: np.ndarray, group_size: int, dtype
     return round_to_dtype(fp8_e4m3fn_decode(codes) * s, dtype)
 
 
+# ---- float4_e2m1f weights: NVFP4 (fp8-e4m3 scales per 16, one global scale) and MXFP4 (e8m0
+# ---- scales per 32) --------------------------------------------------------------------------
+FP4_E2M1_VALUES = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=np.float32)
+
+
+def fp4_e2m1_decode(codes: np.ndarray) -> np.ndarray:
+    """4-bit codes s e e m -> float32: exponent 0 is subnormal (m / 2), bias 1, no inf / NaN
+    (the table the reference builds through float8 in marlin_utils_fp4.py:316-324)."""
+    c = codes.astype(np.int64)
+    mag = FP4_E2M1_VALUES[c & 7]
+    return np.where(c & 8, -mag, mag).astype(np.float32)
+
+
+def _fp4_scale_source_index(size_n: int) -> np.ndarray:
+    """Where each byte of a processed row pair comes from.  The reference regroups two
+    consecutive scale rows (groups 2 g', 2 g' + 1) of the 64-column-permuted matrix so that a
+    thread's eight scales of both groups are 16 adjacent bytes, then swaps the middle two of
+    every four (marlin_utils_fp4.py:41-50, 66-75).  Returns src[F] = rr * N + p0: byte F of the
+    2 N-byte pair block holds element p0 of row rr of the pair."""
+    F = np.arange(2 * size_n)
+    swap = np.array([0, 2, 1, 3])
+    L = (F & ~3) | swap[F & 3]
+    c, rr, jj = L // 16, (L % 16) // 8, L % 8
+    return rr * size_n + 8 * c + jj
+
+
+def nvfp4_process_scales(s_perm: np.ndarray) -> np.ndarray:
+    """Permuted scales [G, N] (non-negative, fp8-e4m3 representable) -> the byte matrix the
+    kernel reads: regrouped (see _fp4_scale_source_index), each value as the high byte of
+    (fp16(s * 2^7) bits << 1): five exponent bits and three mantissa bits
+    (marlin_utils_fp4.py:52-62)."""
+    G, N = s_perm.shape
+    pairs = s_perm.astype(np.float32).reshape(G // 2, 2 * N)[:, _fp4_scale_source_index(N)]
+    bits = (pairs * np.float32(128.0)).astype(np.float16).view(np.uint16)
+    return ((bits >> 7) & 0xFF).astype(np.uint8).reshape(G, N)
+
+
+def nvfp4_unprocess_scales(b: np.ndarray) -> np.ndarray:
+    """Inverse of nvfp4_process_scales: byte matrix [G, N] -> permuted scales (float32)."""
+    G, N = b.shape
+    vals = (b.astype(np.uint16) << 7).view(np.float16).astype(np.float32) / np.float32(128.0)
+    out = np.empty((G // 2, 2 * N), dtype=np.float32)
+    out[:, _fp4_scale_source_index(N)] = vals.reshape(G // 2, 2 * N)
+    return out.reshape(G, N)
+
+
+def mxfp4_process_scales(e_perm: np.ndarray) -> np.ndarray:
+    """Permuted e8m0 exponent bytes [G, N] -> regrouped bytes (marlin_utils_fp4.py:65-77)."""
+    G, N = e_perm.shape
+    return e_perm.reshape(G // 2, 2 * N)[:, _fp4_scale_source_index(N)].reshape(G, N).astype(np.uint8)
+
+
+def mxfp4_unprocess_scales(b: np.ndarray) -> np.ndarray:
+    """Regrouped e8m0 bytes -> permuted scale values 2^(e - 127) (float32)."""
+    G, N = b.shape
+    out = np.empty((G // 2, 2 * N), dtype=np.float32)
+    out[:, _fp4_scale_source_index(N)] = np.exp2(b.astype(np.float32) - 127.0).reshape(G // 2, 2 * N)
+    return out.reshape(G, N)
+
+
+def nvfp4_process_global_scale(g: float, dtype: str) -> np.ndarray:
+    """marlin_utils_fp4.py:80-90: the kernel leaves the fp4 exponent un-rebiased (2^-14 fp16,
+    2^-126 bf16) and the scales carry 2^7; the global scale makes up for both."""
+    bias = 14 if dtype == "float16" else 126
+    return round_to_dtype(np.float32(g) * np.float32(2.0 ** (bias - 7)), dtype)
+
+
+def nvfp4_unprocess_global_scale(g_processed: float, dtype: str) -> np.float32:
+    bias = 14 if dtype == "float16" else 126
+    return np.float32(np.float32(g_processed) * np.float32(2.0 ** (7 - bias)))
+
+
+def dequantize_fp4(codes: np.ndarray, scales: np.ndarray, group_size: int, dtype: str,
+                   global_scale=None) -> np.ndarray:
+    """w[k, n] in the reference's order of roundings (marlin_utils_fp4.py:329-333, 375):
+    dtype( dtype(fp4 * global) * s[g(k), n] ); without a global scale dtype(fp4 * s)."""
+    K = codes.shape[0]
+    g = np.arange(K) // group_size
+    w = fp4_e2m1_decode(codes)
+    if global_scale is not None:
+        w = round_to_dtype(w * round_to_dtype(np.float32(global_scale), dtype), dtype)
+    return round_to_dtype(w * round_to_dtype(scales.astype(np.float32), dtype)[g, :], dtype)
+
+
 def gemm_ref(a: np.ndarray, w: np.ndarray, bias: np.ndarray | None = None) -> np.ndarray:
     """fp32-accumulated product of 16-bit operands held as float32."""
     out = a.astype(np.float32) @ w.astype(np.float32)

@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory from the reference's own
 Python packers (CPU only).
 
-Usage:  python tests/golden/make_golden.py <path-to-reference-checkout> [hqq|fp8|elementwise]
-        (with `hqq` / `fp8` / `elementwise` only that fixture is rewritten)
+Usage:  python tests/golden/make_golden.py <path-to-reference-checkout> [hqq|fp8|fp4|elementwise]
+        (with `hqq` / `fp8` / `fp4` / `elementwise` only that fixture is rewritten)
 
 The reference checkout is only needed to (re)generate the fixtures; the tests
 read the committed ``*.npz`` files and never import the reference.  All inputs
@@ -29,6 +29,11 @@ inputs):
                      (marlin_utils_fp8.py:321-352) with the CUDA repack op replaced by the CPU
                      marlin_weights: codes, scales, weight_ref, packed words, Marlin words,
                      permuted scales with the exponent bias fused in, and the product
+  nvfp4_g16_{f16,bf16}.npz, mxfp4_g32_bf16.npz
+                     float4_e2m1f weights: rand_marlin_weight_nvfp4_like / _mxfp4_like
+                     (marlin_utils_fp4.py:304-397) run on CPU with the CUDA repack op replaced by
+                     the CPU marlin_weights: the random codes, weight_ref, Marlin words, the
+                     processed scale bytes, the processed global scale, and the product
   elementwise_{bf16,f16}.npz
                      the reference's torch implementations of the steps next to the
                      row-parallel GEMM: RMSNorm.forward_static with and without a residual
@@ -106,6 +111,43 @@ def make_fp8(here, mu, mt) -> None:
             out_ref=(a.float() @ weight_ref.T.float()).numpy())
 
 
+def make_fp4(here, mt) -> None:
+    import torch
+    from vllm.model_executor.layers.quantization.utils import marlin_utils_fp4 as f4
+
+    captured = {}
+
+    def cpu_repack(b_q_weight, perm, size_k, size_n, num_bits):
+        # GPTQ words [K / 8, N] -> codes [K, N] -> the CPU Marlin packer
+        shifts = torch.arange(0, 32, num_bits, dtype=torch.int32)
+        codes = ((b_q_weight.unsqueeze(1) >> shifts.view(1, -1, 1)) & ((1 << num_bits) - 1))
+        codes = codes.reshape(size_k, size_n).to(torch.int32)
+        captured["codes"] = codes
+        return mt.marlin_weights(codes, size_k, size_n, num_bits, mt.get_weight_perm(num_bits))
+
+    f4.ops.gptq_marlin_repack = cpu_repack
+    torch.manual_seed(13)
+    for name, dtype, nv, g, M, K, N in (("nvfp4_g16_f16", torch.float16, True, 16, 9, 128, 128),
+                                        ("nvfp4_g16_bf16", torch.bfloat16, True, 16, 23, 256, 192),
+                                        ("mxfp4_g32_bf16", torch.bfloat16, False, 32, 17, 256, 128)):
+        weight = torch.randn((N, K), dtype=dtype)
+        a = torch.randn((M, K), dtype=dtype)
+        if nv:
+            w_ref, q, s, gs = f4.rand_marlin_weight_nvfp4_like(weight, g)
+            gs_bits = _bits16(gs.reshape(1))
+        else:
+            w_ref, q, s = f4.rand_marlin_weight_mxfp4_like(weight, g)
+            gs_bits = np.zeros(0, dtype=np.uint16)
+        np.savez_compressed(
+            os.path.join(here, name + ".npz"),
+            M=np.int64(M), K=np.int64(K), N=np.int64(N), group_size=np.int64(g),
+            is_bf16=np.int64(dtype == torch.bfloat16), is_nvfp4=np.int64(nv), a_bits=_bits16(a),
+            codes=captured["codes"].numpy().astype(np.uint8), marlin_q_w=q.numpy(),
+            marlin_s_bytes=s.contiguous().view(torch.uint8).numpy(), global_scale_bits=gs_bits,
+            w_ref_bits=_bits16(w_ref.contiguous()),
+            out_ref=(a.float() @ w_ref.float()).numpy())
+
+
 def make_elementwise(here) -> None:
     import torch
     from vllm.model_executor.layers.activation import SiluAndMul
@@ -143,6 +185,10 @@ def main(ref_root: str, only: str | None = None) -> None:
     if only == "fp8":
         make_fp8(here, mu, mt)
         print("fp8 fixtures written to", here)
+        return
+    if only == "fp4":
+        make_fp4(here, mt)
+        print("fp4 fixtures written to", here)
         return
     if only == "elementwise":
         make_elementwise(here)
@@ -236,6 +282,7 @@ def main(ref_root: str, only: str | None = None) -> None:
         np.savez_compressed(os.path.join(here, f"gemm_{name}.npz"), **rec)
     make_hqq(here, mu, mt, qu)
     make_fp8(here, mu, mt)
+    make_fp4(here, mt)
     make_elementwise(here)
     print("golden fixtures written to", here)
 

@@ -192,3 +192,30 @@ def test_gptq_layer_parameter_shapes():
     with pytest.raises(ValueError):
         GPTQMarlinConfig(3, 128, False)
     assert GPTQMarlinConfig(4, -1, desc_act=True).desc_act is False
+
+
+def test_fp4_scale_processing_matches_reference_bytes():
+    """This package's nvfp4 / mxfp4 scale and global-scale transforms (torch, CPU) reproduce the
+    bytes the reference's functions produced for the golden fixtures."""
+    import os
+    import torch
+    from oracle import marlin_oracle as mo
+    from vllm_b200 import marlin_utils_fp4 as f4
+    golden = os.path.join(os.path.dirname(__file__), "golden")
+    for name in ("nvfp4_g16_f16", "nvfp4_g16_bf16", "mxfp4_g32_bf16"):
+        g = np.load(os.path.join(golden, name + ".npz"))
+        bf, nv = bool(g["is_bf16"]), bool(g["is_nvfp4"])
+        td = torch.bfloat16 if bf else torch.float16
+        b = g["marlin_s_bytes"]
+        if nv:
+            s_perm = torch.from_numpy(mo.nvfp4_unprocess_scales(b)).to(td)
+            got = f4.nvfp4_marlin_process_scales(s_perm).view(torch.uint8).numpy()
+            bits = np.asarray(g["global_scale_bits"], dtype=np.uint16)
+            gp = (bits.astype(np.uint32) << 16).view(np.float32) if bf else bits.view(np.float16).astype(np.float32)
+            gl = mo.nvfp4_unprocess_global_scale(gp[0], "bfloat16" if bf else "float16")
+            again = f4.nvfp4_marlin_process_global_scale(torch.tensor(float(gl), dtype=td))
+            assert float(again) == float(gp[0])
+        else:
+            s_perm = torch.from_numpy(mo.mxfp4_unprocess_scales(b)).to(td)
+            got = f4.mxfp4_marlin_process_scales(s_perm).view(torch.uint8).numpy()
+        assert np.array_equal(got, b), name

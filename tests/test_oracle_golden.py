@@ -176,3 +176,38 @@ def test_fp8_decode_known_values():
     want = [0.0, 2.0 ** -9, 7 * 2.0 ** -9, 2.0 ** -6, 1.0, 448.0, -0.0, -1.0, -448.0]
     assert mo.fp8_e4m3fn_decode(c).tolist() == want
     assert np.isnan(mo.fp8_e4m3fn_decode(np.array([0x7F, 0xFF], dtype=np.uint8))).all()
+
+
+@pytest.mark.parametrize("name", ["nvfp4_g16_f16", "nvfp4_g16_bf16", "mxfp4_g32_bf16"])
+def test_fp4_weights_match_reference(name):
+    """float4_e2m1f weights (NVFP4 / MXFP4): Marlin words, the processed scale bytes and global
+    scale decoded back to values, and the dequantised weights of the reference's
+    rand_marlin_weight_nvfp4_like / _mxfp4_like; the forward transforms reproduce the bytes."""
+    g = _load(name + ".npz")
+    K, N, gs, bf = int(g["K"]), int(g["N"]), int(g["group_size"]), bool(g["is_bf16"])
+    nv = bool(g["is_nvfp4"])
+    dtype = "bfloat16" if bf else "float16"
+    codes = g["codes"]
+    assert np.array_equal(mo.marlin_weights(codes.astype(np.int32), 4), g["marlin_q_w"])
+    b = g["marlin_s_bytes"]
+    assert b.shape == (K // gs, N)
+    if nv:
+        s = mo.marlin_unpermute_scales(mo.nvfp4_unprocess_scales(b), K, N, gs)
+        gl = mo.nvfp4_unprocess_global_scale(_f16(g["global_scale_bits"], bf)[0], dtype)
+        w = mo.dequantize_fp4(codes, s, gs, dtype, global_scale=gl)
+        assert np.array_equal(mo.nvfp4_process_scales(mo.marlin_permute_scales(s, K, N, gs)), b)
+        assert float(np.ravel(mo.nvfp4_process_global_scale(gl, dtype))[0]) == float(_f16(g["global_scale_bits"], bf)[0])
+    else:
+        s = mo.marlin_unpermute_scales(mo.mxfp4_unprocess_scales(b), K, N, gs)
+        w = mo.dequantize_fp4(codes, s, gs, dtype)
+        e = np.round(np.log2(mo.marlin_permute_scales(s, K, N, gs))).astype(np.int64) + 127
+        assert np.array_equal(mo.mxfp4_process_scales(e.astype(np.uint8)), b)
+    assert np.array_equal(w, _f16(g["w_ref_bits"], bf))
+    out = mo.gemm_ref(_f16(g["a_bits"], bf), w)
+    assert np.allclose(out, g["out_ref"], rtol=1e-5, atol=1e-4)
+
+
+def test_fp4_decode_table():
+    c = np.arange(16, dtype=np.uint8)
+    want = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
+    assert mo.fp4_e2m1_decode(c).tolist() == want

@@ -24,6 +24,7 @@ EXPORTS = (
     "b200q_marlin_gemm_scratch_bytes",
     "b200q_marlin_gemm_preferred_scratch_bytes",
     "b200q_marlin_gemm",
+    "b200q_marlin_gemm_fp4",
     "b200q_marlin_gemm_noalloc_max_scratch",
     "b200q_marlin_gemm_noalloc",
     "b200q_all_reduce_state_bytes",
@@ -39,6 +40,7 @@ EXPORTS = (
 OK, EINVAL, EUNSUPPORTED, ECUDA, ESCRATCH = 0, -1, -2, -3, -4
 F16, BF16 = 0, 1
 FLAG_K_FULL, FLAG_ATOMIC_ADD, FLAG_FP32_REDUCE, FLAG_ZP_FLOAT = 1, 2, 4, 8
+FP4_SCALES_E4M3, FP4_SCALES_E8M0 = 1, 2
 
 _lib = None
 
@@ -83,6 +85,9 @@ def load() -> ctypes.CDLL:
     lib.b200q_marlin_gemm.argtypes = [
         vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, c.c_size_t, vp, i64, i64, i32,
         i64, i64, i64, i64, u32, vp]
+    lib.b200q_marlin_gemm_fp4.restype = i32
+    lib.b200q_marlin_gemm_fp4.argtypes = [
+        vp, i64, vp, vp, vp, i32, vp, vp, vp, c.c_size_t, vp, i64, i32, i64, i64, i64, i64, vp]
     lib.b200q_marlin_gemm_all_reduce.restype = i32
     lib.b200q_marlin_gemm_all_reduce.argtypes = [
         vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, c.c_size_t, vp, i64, i64, i32,

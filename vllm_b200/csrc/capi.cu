@@ -168,19 +168,22 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
                      const void* b_bias, void* c, void* scratch, size_t scratch_bytes,
                      int32_t* workspace, int64_t workspace_len, int64_t b_q_type_id, int a_dtype,
                      int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups,
-                     unsigned flags, cudaStream_t stream, const ArLink* link) {
+                     unsigned flags, cudaStream_t stream, const ArLink* link,
+                     const void* global_scale = nullptr, int fp4_scales = 0) {
   // ---- type contract ---------------------------------------------------------------
   int bits = 0;
   bool type_has_zp = false;
   bool w_fp8 = false;
+  bool w_fp4 = false;
   if (b_q_type_id == kTypeU4B8) { bits = 4; }
   else if (b_q_type_id == kTypeU8B128) { bits = 8; }
   else if (b_q_type_id == kTypeU4) { bits = 4; type_has_zp = true; }
   else if (b_q_type_id == kTypeU8) { bits = 8; type_has_zp = true; }
   else if (b_q_type_id == kTypeFE4M3fn) { bits = 8; w_fp8 = true; }
+  else if (b_q_type_id == kTypeFE2M1f) { bits = 4; w_fp4 = true; }
   else {
-    set_error("b_q_type id %lld is not supported (uint4b8, uint8b128, uint4, uint8, float8_e4m3fn)",
-              (long long)b_q_type_id);
+    set_error("b_q_type id %lld is not supported (uint4b8, uint8b128, uint4, uint8, float8_e4m3fn, "
+              "float4_e2m1f)", (long long)b_q_type_id);
     return B200Q_EUNSUPPORTED;
   }
   const bool has_zp = b_zeros != nullptr;
@@ -281,8 +284,30 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
                   "float zero-points need grouped scales without act_order");
   if (w_fp8)
     B200Q_REQUIRE(!has_act_order, B200Q_EUNSUPPORTED, "float8_e4m3fn weights with act_order");
-  // these two run the reference-order kernel at every row count
-  const bool general_only = zp_float || w_fp8;
+  if (w_fp4) {
+    // gptq_marlin.cu:818-829, 907-917: fp8-e4m3 scales per 16 values + a global scale (NVFP4),
+    // or e8m0 scales per 32 values (MXFP4)
+    B200Q_REQUIRE(fp4_scales == 1 || fp4_scales == 2, B200Q_EINVAL,
+                  "float4_e2m1f weights come through b200q_marlin_gemm_fp4 (8-bit scales)");
+    B200Q_REQUIRE(!has_act_order && gm == kGrouped, B200Q_EUNSUPPORTED,
+                  "float4_e2m1f weights need grouped scales without act_order");
+    const int64_t group_size = size_k / num_groups;
+    B200Q_REQUIRE(group_size == (fp4_scales == 1 ? 16 : 32), B200Q_EINVAL,
+                  "float4_e2m1f only supports group_size == 16 (NVFP4) and group_size == 32 (MXFP4)");
+    B200Q_REQUIRE(num_groups % 2 == 0, B200Q_EUNSUPPORTED,
+                  "float4_e2m1f scales are laid out in pairs of groups: num_groups = %lld is odd",
+                  (long long)num_groups);
+    B200Q_REQUIRE((fp4_scales == 1) == (global_scale != nullptr), B200Q_EINVAL,
+                  fp4_scales == 1 ? "the global_scale parameter must be passed for nvfp4 format."
+                                  : "global_scale can only be used for nvfp4 format.");
+    B200Q_REQUIRE(fp4_scales == 1 || a_dtype == B200Q_BF16, B200Q_EUNSUPPORTED,
+                  "e8m0 scales (MXFP4) need bfloat16 activations");
+  } else {
+    B200Q_REQUIRE(global_scale == nullptr && fp4_scales == 0, B200Q_EINVAL,
+                  "global_scale can only be used for nvfp4 format.");
+  }
+  // these run the reference-order kernel at every row count
+  const bool general_only = zp_float || w_fp8 || w_fp4;
   // ---- prefill regime: tensor-core kernel ----------------------------------------------
   if (!general_only && tc_path_enabled() && group_blocks >= 2 && tc_gemm_supported(size_m, size_n, size_k, gm)) {
     int rc = launch_tc_gemm(a_used, lda_used, b_q_weight, b_scales, b_zeros, b_bias, c, a_dtype,
@@ -327,6 +352,8 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
     p.num_groups = (int)num_groups;
     p.zp_float = zp_float ? 1 : 0;
     p.w_fp8 = w_fp8 ? 1 : 0;
+    p.w_fp4 = w_fp4 ? fp4_scales : 0;
+    p.global_scale = global_scale;
     p.ar = ArLink{};
     if (fuse_ar) p.ar = *link;
     int rc;
@@ -357,6 +384,20 @@ extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q
   return gemm_impl(a, lda, b_q_weight, b_scales, b_zeros, g_idx, perm, b_bias, c, scratch,
                    scratch_bytes, workspace, workspace_len, b_q_type_id, a_dtype, size_m, size_n,
                    size_k, num_groups, flags, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+extern "C" int b200q_marlin_gemm_fp4(const void* a, int64_t lda, const uint32_t* b_q_weight,
+                                     const void* b_scales, const void* global_scale, int scale_kind,
+                                     const void* b_bias, void* c, void* scratch, size_t scratch_bytes,
+                                     int32_t* workspace, int64_t workspace_len, int a_dtype,
+                                     int64_t size_m, int64_t size_n, int64_t size_k,
+                                     int64_t num_groups, b200q_stream_t stream) {
+  B200Q_REQUIRE(scale_kind == B200Q_FP4_SCALES_E4M3 || scale_kind == B200Q_FP4_SCALES_E8M0,
+                B200Q_EINVAL, "scale_kind must be B200Q_FP4_SCALES_E4M3 or B200Q_FP4_SCALES_E8M0");
+  return gemm_impl(a, lda, b_q_weight, b_scales, nullptr, nullptr, nullptr, b_bias, c, scratch,
+                   scratch_bytes, workspace, workspace_len, kTypeFE2M1f, a_dtype, size_m, size_n,
+                   size_k, num_groups, B200Q_FLAG_K_FULL, static_cast<cudaStream_t>(stream), nullptr,
+                   global_scale, scale_kind);
 }
 
 extern "C" int b200q_marlin_gemm_all_reduce(

@@ -38,6 +38,7 @@ constexpr int64_t kTypeU4B8 = 4ll << 8 | 8ll << 17 | 1ll << 50;
 constexpr int64_t kTypeU4 = 4ll << 8 | 1ll << 50;
 constexpr int64_t kTypeU8B128 = 8ll << 8 | 128ll << 17 | 1ll << 50;
 constexpr int64_t kTypeFE4M3fn = 2814749767172868ll;  // float8_e4m3fn (csrc/core/scalar_type.hpp)
+constexpr int64_t kTypeFE2M1f = 562949953487106ll;    // float4_e2m1f
 constexpr int64_t kTypeU8 = 8ll << 8 | 1ll << 50;
 
 // bump the process-wide launch counter (b200q_kernel_launches)

@@ -12,6 +12,8 @@
 // reset on the way out) adds them up and writes C.
 #pragma once
 
+#include <type_traits>
+
 #include "gemm_params.cuh"
 
 namespace b200q {
@@ -40,9 +42,17 @@ struct LookupCfg {
 
 // FP8: the 8-bit codes are float8_e4m3fn values; the scales carry the exponent re-bias factor
 // (2^8 for fp16, 2^120 for bf16), as the reference's host code prepares them.
+// FP4: the 4-bit codes are float4_e2m1f values (sign, two exponent bits, one mantissa bit); the
+// scales are bytes in the regrouped layout of the reference's host code (a lane's eight scales of
+// both groups of a pair are 16 adjacent bytes).  NVFP4 (p.w_fp4 = 1): the exponent field is moved
+// into the 16-bit format without re-biasing and the scale bytes expand to s * 2^7; the global
+// scale, applied to the fp32 sums, carries the two corrections (dequant.h:398-414, 470-499,
+// marlin_template.h:1180-1188, 1500-1502).  MXFP4 (2): the weights are re-biased exactly and the
+// scale bytes are bf16 exponent fields (dequant.h:452-468, 501-513).
 template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, int MINB, bool ZPF = false,
-          bool FP8 = false>
+          bool FP8 = false, bool FP4 = false>
 __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const StreamParams p) {
+  static_assert(!FP4 || (BITS == 4 && !HAS_ZP && GM == kGrouped && !FP8), "fp4 weights: grouped scales");
   static_assert(!ZPF || (HAS_ZP && GM == kGrouped), "float zero-points come with grouped scales");
   static_assert(!FP8 || (BITS == 8 && !HAS_ZP && GM != kLookup), "fp8 weights: 8 bits, no zero-points");
   using Cfg = LookupCfg<BITS, HAS_ZP, GM, MB, NTW, ZPF>;
@@ -126,7 +136,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
         }
         if (has_scales(kt)) {
           const int g = kt / p.group_blocks;
-          if (GM == kGrouped && lane < NTW * 8)
+          if (GM == kGrouped && !FP4 && lane < NTW * 8)
             cp_async16(st + Cfg::kSOff + lane * 16, S + (size_t)g * p.n + nt0 * 64 + lane * 8);
           if (ZPF) {
             if (lane < NTW * 8)
@@ -150,10 +160,29 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
     (void)sdup;
     (void)zdup;
 
-    auto load_group_from_stage = [&](uint32_t st) {
+    auto load_group_from_stage = [&](uint32_t st, int kt) {
 #pragma unroll
       for (int j = 0; j < NTW; ++j) {
-        if (GM == kGrouped) {
+        if (FP4) {
+          // this lane's eight scale bytes of the group: byte 4 (sub / 2) + 2 h + sub % 2 belongs
+          // to column 16 sub + c8 + 8 h of the tile
+          const int g = kt / p.group_blocks;
+          const unsigned char* src = reinterpret_cast<const unsigned char*>(p.scales) +
+                                     (size_t)(g & ~1) * p.n + 16 * (8 * (nt0 + j) + c8) + 8 * (g & 1);
+          const uint2 raw = __ldg(reinterpret_cast<const uint2*>(src));
+          const uint32_t word[2] = {raw.x, raw.y};
+#pragma unroll
+          for (int sub = 0; sub < 4; ++sub)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t b = (word[sub >> 1] >> (8 * (2 * h + (sub & 1)))) & 0xffu;
+              uint32_t v;
+              if (p.w_fp4 == 2) v = b << 7;                                         // e8m0 -> bf16 exponent
+              else if (std::is_same<T, half>::value) v = b << 7;                    // S0E5M3 -> fp16 bits 14..7
+              else v = ((b & 0x80u) << 7) | ((b & 0x7fu) << 4);                     // -> bf16: top bit, then 7 bits
+              sdup[j][2 * sub + h] = v | (v << 16);
+            }
+        } else if (GM == kGrouped) {
           const uint4 s4 = lds128(st + Cfg::kSOff + j * 128 + c8 * 16);
           const uint32_t sv[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
@@ -213,7 +242,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
       issue(kt + D - 1, (kt - wb + D - 1) % D);
       const uint32_t st = ring + stage * Cfg::kStageBytes;
 
-      if (has_scales(kt)) load_group_from_stage(st);
+      if (has_scales(kt)) load_group_from_stage(st, kt);
 
       uint32_t afrag[MB][4];
       {
@@ -241,7 +270,21 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
 #pragma unroll
         for (int sub = 0; sub < 4; ++sub) {
           uint32_t f[4];  // block 0: f[0] rows lo, f[1] rows hi; block 1: f[2], f[3]
-          if (BITS == 4) {
+          if (FP4) {
+            // nibble i of the word sits where the uint4 codes do: f[i] takes nibbles i and i + 4
+            constexpr int kShift = std::is_same<T, half>::value ? 3 : 6;
+            const uint32_t q = w[sub];
+            auto conv = [](uint32_t x) { return (x & 0x80008000u) | ((x & 0x70007000u) >> kShift); };
+            f[3] = conv(q);
+            f[2] = conv(q << 4);
+            f[1] = conv(q << 8);
+            f[0] = conv(q << 12);
+            if (p.w_fp4 == 2) {
+              // exact re-bias: 2^126 as a bfloat16 pair
+#pragma unroll
+              for (int e = 0; e < 4; ++e) f[e] = Pair<T>::mul(f[e], 0x7e807e80u);
+            }
+          } else if (BITS == 4) {
             dequant4<T, !HAS_ZP>(w[sub], f);
           } else {
             uint32_t t0[2], t1[2];
@@ -390,6 +433,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
       for (int e = 0; e < Cfg::kEpt; ++e) {
         cs[e] = (GM == kChannel) ? Pair<T>::to_float(S[single_perm_pos(n_base + e)]) : 1.f;
         if (FP8 && GM == kChannel) cs[e] *= Fp8Cvt<T>::kRebiasInv;
+        if (FP4 && p.w_fp4 == 1) cs[e] = Pair<T>::to_float(*static_cast<const uint16_t*>(p.global_scale));
         bs[e] = p.bias ? Pair<T>::to_float(
                              static_cast<const uint16_t*>(p.bias)[single_perm_pos(n_base + e)])
                        : 0.f;
@@ -419,11 +463,12 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
 }
 
 // Host launcher for one (type, bits, zp, group mode, MB, NTW) variant.
-template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, bool ZPF = false, bool FP8 = false>
+template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, bool ZPF = false, bool FP8 = false,
+          bool FP4 = false>
 int launch_lookup(const StreamParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = LookupCfg<BITS, HAS_ZP, GM, MB, NTW, ZPF>;
   constexpr int kMinBlocks = (MB * NTW <= 2 && Cfg::kSmemBytes <= 112 * 1024) ? 2 : 1;
-  auto kernel = gemm_lookup_kernel<T, BITS, HAS_ZP, GM, MB, NTW, kMinBlocks, ZPF, FP8>;
+  auto kernel = gemm_lookup_kernel<T, BITS, HAS_ZP, GM, MB, NTW, kMinBlocks, ZPF, FP8, FP4>;
   static bool attr_done[64] = {};  // per device; benign race: the call is idempotent
   int dev = 0;
   B200Q_CUDA_OK(cudaGetDevice(&dev));

@@ -30,6 +30,9 @@ struct StreamParams {
   int num_groups;
   int zp_float;            // zeros holds 16-bit floats [G, N] in the scales' layout
   int w_fp8;               // the 8-bit codes are float8_e4m3fn values
+  int w_fp4;               // the 4-bit codes are float4_e2m1f values; scales are bytes [G, N] in
+                           // the regrouped layout: 1 = fp8 S0E5M3 (NVFP4), 2 = e8m0 (MXFP4)
+  const void* global_scale;  // NVFP4: one 16-bit value (with the exponent corrections folded in)
   // weight-embedding constants of the streaming kernel (filled by its launcher)
   uint32_t c_ex, c_mask_lo, c_mask_hi;
   // when ar.world > 0 the streaming kernel all-reduces its output over the link

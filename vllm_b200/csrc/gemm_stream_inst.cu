@@ -88,6 +88,20 @@ int fp8_weights(const StreamParams& p, int gm, int rows8, int ntw, int max_ctas,
   return B200Q_EUNSUPPORTED;
 }
 
+// float4_e2m1f weights (NVFP4 / MXFP4): the reference-order kernel for every row count
+int fp4_weights(const StreamParams& p, int gm, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
+  if constexpr (B == 4) {
+    if (ntw != 1 || gm != kGrouped) return B200Q_EUNSUPPORTED;
+    const int mb = (rows8 + 1) / 2;  // 16-row blocks
+    switch (mb) {
+      case 1: return launch_lookup<T, B, false, kGrouped, 1, 1, false, false, true>(p, max_ctas, stream);
+      case 2: return launch_lookup<T, B, false, kGrouped, 2, 1, false, false, true>(p, max_ctas, stream);
+      case 4: return launch_lookup<T, B, false, kGrouped, 4, 1, false, false, true>(p, max_ctas, stream);
+    }
+  }
+  return B200Q_EUNSUPPORTED;
+}
+
 int lookup(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
   if (ntw != 1) return B200Q_EUNSUPPORTED;
   const int mb = (rows8 + 1) / 2;  // 16-row blocks
@@ -105,6 +119,7 @@ template <>
 int dispatch_stream<InstT, INST_BITS>(const StreamParams& p, bool has_zp, int gm, int mb, int ntw,
                                       int max_ctas, cudaStream_t stream) {
   if (p.w_fp8) return has_zp ? B200Q_EUNSUPPORTED : fp8_weights(p, gm, mb, ntw, max_ctas, stream);
+  if (p.w_fp4) return has_zp ? B200Q_EUNSUPPORTED : fp4_weights(p, gm, mb, ntw, max_ctas, stream);
   if (p.zp_float)
     return (has_zp && gm == kGrouped) ? grouped_zp_float(p, mb, ntw, max_ctas, stream)
                                       : B200Q_EUNSUPPORTED;

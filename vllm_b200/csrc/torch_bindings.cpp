@@ -64,6 +64,8 @@ at::Tensor& scratch_for(const at::Device& dev, cudaStream_t stream, size_t bytes
 
 struct GemmArgs {
   const void *a, *scales, *bias;
+  const void* global_scale;  // NVFP4
+  int fp4_scales;            // 0, or B200Q_FP4_SCALES_* for float4_e2m1f weights
   const uint32_t *b, *zeros;
   const int32_t *g_idx, *perm;
   int64_t lda, num_groups;
@@ -108,7 +110,19 @@ at::Tensor check_gemm(const at::Tensor& a, const std::optional<at::Tensor>& c_or
   TORCH_CHECK(b_scales.is_contiguous(), "b_scales is not contiguous");
   TORCH_CHECK(a.scalar_type() == at::kHalf || a.scalar_type() == at::kBFloat16,
               "gpt_marlin_gemm only supports bfloat16 and float16");
-  TORCH_CHECK(b_scales.scalar_type() == a.scalar_type(), "b_scales must have the dtype of a");
+  // float4_e2m1f weights carry 8-bit scales: float8_e4m3fn per 16 values (NVFP4) or
+  // float8_e8m0fnu per 32 (MXFP4) (gptq_marlin.cu:907-917)
+  const bool is_fp4 = qt.is_float && qt.bits == 4;
+  g->fp4_scales = 0;
+  g->global_scale = nullptr;
+  if (is_fp4) {
+    if (b_scales.scalar_type() == at::kFloat8_e4m3fn) g->fp4_scales = B200Q_FP4_SCALES_E4M3;
+    else if (b_scales.scalar_type() == at::kFloat8_e8m0fnu) g->fp4_scales = B200Q_FP4_SCALES_E8M0;
+    else TORCH_CHECK(false, "float4_e2m1f only supports group_size == 16 (NVFP4) ",
+                     "and group_size == 32 (MXFP4): b_scales must be float8_e4m3fn or float8_e8m0fnu");
+  } else {
+    TORCH_CHECK(b_scales.scalar_type() == a.scalar_type(), "b_scales must have the dtype of a");
+  }
 
   at::Tensor c;
   if (c_or_none.has_value()) {
@@ -149,7 +163,17 @@ at::Tensor check_gemm(const at::Tensor& a, const std::optional<at::Tensor>& c_or
       g->act_order = true;
     }
   }
-  TORCH_CHECK(!global_scale.has_value(), "global_scale can only be used for nvfp4 format.");
+  if (global_scale.has_value()) {
+    TORCH_CHECK(g->fp4_scales == B200Q_FP4_SCALES_E4M3,
+                "global_scale can only be used for nvfp4 format.");
+    const at::Tensor& gs = global_scale.value();
+    TORCH_CHECK(gs.is_cuda() && gs.numel() == 1 && gs.scalar_type() == a.scalar_type(),
+                "global_scale must be one value of the dtype of a, on the GPU");
+    g->global_scale = gs.data_ptr();
+  } else {
+    TORCH_CHECK(g->fp4_scales != B200Q_FP4_SCALES_E4M3,
+                "the global_scale parameter must be passed for nvfp4 format.");
+  }
 
   g->bias = nullptr;
   if (b_bias_or_none.has_value()) {
@@ -230,10 +254,20 @@ at::Tensor gptq_marlin_gemm(at::Tensor& a, std::optional<at::Tensor> c_or_none,
   const size_t nbytes =
       b200q_marlin_gemm_preferred_scratch_bytes(size_m, size_n, size_k, g.act_order ? 1 : 0);
   at::Tensor& scratch = scratch_for(a.device(), stream, nbytes);
-  const int rc = b200q_marlin_gemm(g.a, g.lda, g.b, g.scales, g.zeros, g.g_idx, g.perm, g.bias,
-                                   c.data_ptr(), scratch.data_ptr(), (size_t)scratch.numel(),
-                                   workspace.data_ptr<int32_t>(), workspace.numel(), b_q_type,
-                                   g.dtype, size_m, size_n, size_k, g.num_groups, g.flags, stream);
+  int rc;
+  if (g.fp4_scales != 0) {
+    TORCH_CHECK(g.zeros == nullptr && !g.act_order,
+                "float4_e2m1f weights take neither zero-points nor act_order");
+    rc = b200q_marlin_gemm_fp4(g.a, g.lda, g.b, g.scales, g.global_scale, g.fp4_scales, g.bias,
+                               c.data_ptr(), scratch.data_ptr(), (size_t)scratch.numel(),
+                               workspace.data_ptr<int32_t>(), workspace.numel(), g.dtype, size_m,
+                               size_n, size_k, g.num_groups, stream);
+  } else {
+    rc = b200q_marlin_gemm(g.a, g.lda, g.b, g.scales, g.zeros, g.g_idx, g.perm, g.bias,
+                           c.data_ptr(), scratch.data_ptr(), (size_t)scratch.numel(),
+                           workspace.data_ptr<int32_t>(), workspace.numel(), b_q_type, g.dtype,
+                           size_m, size_n, size_k, g.num_groups, g.flags, stream);
+  }
   B200Q_TORCH_OK(rc, "gptq_marlin_gemm");
   return c;
 }
@@ -256,6 +290,7 @@ at::Tensor gptq_marlin_gemm_all_reduce(
                             b_zeros_or_none, g_idx_or_none, perm_or_none, workspace, b_q_type,
                             size_m, size_n, size_k, is_k_full, use_atomic_add, use_fp32_reduce,
                             is_zp_float, &g);
+  TORCH_CHECK(g.fp4_scales == 0, "gptq_marlin_gemm_all_reduce does not take float4_e2m1f weights");
   if (size_m == 0) return c;
   TORCH_CHECK(peer_ptrs.is_cuda() && peer_ptrs.scalar_type() == at::kLong &&
                   peer_ptrs.numel() >= world,

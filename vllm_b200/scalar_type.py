@@ -70,8 +70,10 @@ class ScalarType:
 
     def __str__(self) -> str:
         if self.is_floating_point():
+            # flags (vllm/scalar_type.py:218-246): f = finite values only, n = NaNs in a
+            # non-IEEE encoding (nan_repr != NONE = 0)
             return f"float{self.size_bits}_e{self.exponent}m{self.mantissa}" + (
-                "fn" if self._finite_values_only else "")
+                "f" if self._finite_values_only else "") + ("n" if self.nan_repr != 0 else "")
         s = f"uint{self.size_bits}" if not self.signed else f"int{self.size_bits}"
         return s + (f"b{self.bias}" if self.bias else "")
 
@@ -83,7 +85,9 @@ class scalar_types:
     uint8b128 = ScalarType.uint(8, 128)
     # NanRepr.EXTD_RANGE_MAX_MIN = 2 (vllm/scalar_type.py:14-20,338-340)
     float8_e4m3fn = ScalarType.float_(4, 3, True, 2)
+    # NanRepr.NONE = 0 (vllm/scalar_type.py:345): NVFP4 / MXFP4 weight codes
+    float4_e2m1f = ScalarType.float_(2, 1, True, 0)
 
 
 _ALL = (scalar_types.uint4, scalar_types.uint8, scalar_types.uint4b8, scalar_types.uint8b128,
-        scalar_types.float8_e4m3fn)
+        scalar_types.float8_e4m3fn, scalar_types.float4_e2m1f)
