@@ -460,6 +460,8 @@ def run_ours(args, world, rank, local_rank):
             g4, n4g = time_shapes([(p, m) for p, m in shapes4 if p.row_parallel], steps4, reduce=False)
             launches += n4g
         extra["config4"] = (shapes4, t4, g4, steps4)
+    if os.environ.get("BENCH_NO_FP4", "0") != "1":
+        extra["fp4"] = time_fp4(torch, ops, dev, dt, stream, gen, ws, min(args.steps, 10))
     decode = run_decode(world, rank, dev) if os.environ.get("BENCH_NO_DECODE", "0") != "1" else None
     if rank == 0:
         report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, decode,
@@ -471,6 +473,49 @@ def run_ours(args, world, rank, local_rank):
         torch.cuda.synchronize()
         sys.stdout.flush()
         os._exit(0)
+
+
+def time_fp4(torch, ops, dev, dt, stream, gen, ws, steps):
+    """NVFP4 (float4_e2m1f weights, float8_e4m3fn scales per 16 values, one global scale) on the
+    Llama-3-8B gate_up shape through the torch operator, device-resident inputs, a CUDA graph of
+    `steps` calls over rotating weight copies: us per call at M = 1, 16, 64, 1024.  Random codes
+    and scale bytes of the processed form (the kernel's time does not depend on the values)."""
+    from vllm_b200.scalar_type import scalar_types
+    k, n, group = 4096, 28672, 16
+    copies = 8
+    qs = [torch.randint(-2**31, 2**31 - 1, (k // 16, n * 2), dtype=torch.int32, device=dev,
+                        generator=gen) for _ in range(copies)]
+    # scale bytes: exponent field 0b1xxxx (what non-zero scales look like after processing)
+    ss = [(torch.randint(0, 64, (k // group, n), dtype=torch.uint8, device=dev, generator=gen) | 0x80)
+          .view(torch.float8_e4m3fn) for _ in range(copies)]
+    gs = torch.full((1,), 2.0 ** -7, dtype=dt, device=dev)
+    rows = []
+    for m in (1, 16, 64, 1024):
+        a = torch.randn((m, k), dtype=dt, device=dev, generator=gen)
+
+        def body():
+            for i in range(steps):
+                ops.gptq_marlin_gemm(a, None, qs[i % copies], None, ss[i % copies], gs, None, None, None,
+                                     ws, scalar_types.float4_e2m1f, m, n, k)
+        with torch.cuda.stream(stream):
+            body()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            body()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            g.replay()
+            e0.record()
+            g.replay()
+            e1.record()
+        torch.cuda.synchronize()
+        us = 1e3 * e0.elapsed_time(e1) / steps
+        b = k * n // 2 + (k // group) * n + 2 * m * k + 2 * m * n      # weights, scale bytes, A, C
+        rows.append({"m": m, "us": round(us, 2), "gbs": round(b / us / 1e3, 1),
+                     "tflops": round(2.0 * m * n * k / us / 1e6, 2)})
+    return {"workload": "nvfp4 (float4_e2m1f, group 16) gate_up 4096->28672, reference-order kernel",
+            "steps": steps, "per_shape": rows}
 
 
 def run_ar_check(torch, dist, D, lib, dev, custom_ar, ar_link, rank, world):
@@ -689,6 +734,10 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, 
                         "8192->57344/tp (column-parallel), down 28672/tp->8192 (row-parallel + "
                         "all-reduce)" % world,
             "m_values": MS4, "steps": steps4, "per_shape": rows4}
+    if "fp4" in extra:
+        for row in extra["fp4"]["per_shape"]:
+            row["frac_hbm"] = round(row["gbs"] / peaks["hbm_gbs"], 3)
+        line["fp4"] = extra["fp4"]
     if world == 1 and e2e_steps:
         b, s = cpu_sample(LAYERS, 16)
         line["cpu_baseline"] = {
@@ -730,7 +779,7 @@ def main():
         MS = [int(m)]
         if not LAYERS:
             raise SystemExit("--only: unknown layer %r" % name)
-        for key in ("BENCH_NO_DECODE", "BENCH_NO_CONFIG4", "BENCH_NO_E2E"):
+        for key in ("BENCH_NO_DECODE", "BENCH_NO_CONFIG4", "BENCH_NO_E2E", "BENCH_NO_FP4"):
             os.environ[key] = "1"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     world = int(os.environ.get("WORLD_SIZE", "1"))
