@@ -462,6 +462,7 @@ def run_ours(args, world, rank, local_rank):
         extra["config4"] = (shapes4, t4, g4, steps4)
     if os.environ.get("BENCH_NO_FP4", "0") != "1":
         extra["fp4"] = time_fp4(torch, ops, dev, dt, stream, gen, ws, min(args.steps, 10))
+        extra["moe"] = time_moe(torch, ops, dev, dt, stream, gen, ws, min(args.steps, 10))
     decode = run_decode(world, rank, dev) if os.environ.get("BENCH_NO_DECODE", "0") != "1" else None
     if rank == 0:
         report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, decode,
@@ -516,6 +517,56 @@ def time_fp4(torch, ops, dev, dt, stream, gen, ws, steps):
                      "tflops": round(2.0 * m * n * k / us / 1e6, 2)})
     return {"workload": "nvfp4 (float4_e2m1f, group 16) gate_up 4096->28672, reference-order kernel",
             "steps": steps, "per_shape": rows}
+
+
+def time_moe(torch, ops, dev, dt, stream, gen, ws, steps):
+    """moe_wna16_marlin_gemm on a Mixtral-8x7B-shaped gate_up projection (8 experts, top-2,
+    4096 -> 2 x 14336, uint4b8 g128): us per call at 16 and 256 tokens, device-resident inputs,
+    a CUDA graph of `steps` calls over two weight sets (940 MB: larger than L2).  The bytes counted
+    are the weights and scales of the experts that received tokens."""
+    from vllm_b200 import fused_moe
+    from vllm_b200.scalar_type import scalar_types
+    e, topk, k, n, group = 8, 2, 4096, 28672, 128
+    qs = [torch.randint(-2**31, 2**31 - 1, (e, k // 16, n * 2), dtype=torch.int32, device=dev,
+                        generator=gen) for _ in range(2)]
+    ss = [(torch.rand((e, k // group, n), device=dev, generator=gen) * 0.018 + 0.002).to(dt)
+          for _ in range(2)]
+    rows = []
+    for m in (16, 256):
+        a = torch.randn((m, k), dtype=dt, device=dev, generator=gen)
+        topk_ids = torch.stack([torch.randperm(e, device=dev, generator=gen)[:topk] for _ in range(m)])
+        tw = torch.rand((m * topk,), device=dev, generator=gen)
+        for bs in (8, 16, 32, 48, 64):
+            if m * topk / e / bs < 0.9:
+                break
+        sorted_ids, expert_ids, num = fused_moe.moe_align_block_size(topk_ids.to(torch.int32), bs, e)
+        used = int(torch.unique(topk_ids).numel())
+
+        def body():
+            for i in range(steps):
+                ops.moe_wna16_marlin_gemm(a, None, qs[i % 2], None, ss[i % 2], None, None, None, None, ws,
+                                          sorted_ids, expert_ids, num, tw, bs, topk, False, False,
+                                          scalar_types.uint4b8, m, n, k)
+        with torch.cuda.stream(stream):
+            body()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            body()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            g.replay()
+            e0.record()
+            g.replay()
+            e1.record()
+        torch.cuda.synchronize()
+        us = 1e3 * e0.elapsed_time(e1) / steps
+        b = used * (k * n // 2 + (k // group) * n * 2) + 2 * m * k + 2 * m * topk * n
+        rows.append({"tokens": m, "block": bs, "experts_used": used, "us": round(us, 2),
+                     "gbs": round(b / us / 1e3, 1),
+                     "tflops": round(2.0 * m * topk * n * k / us / 1e6, 2)})
+    return {"workload": "moe_wna16_marlin_gemm: 8 experts, top-2, gate_up 4096 -> 28672, uint4b8 g128, "
+                        "reference-order kernel", "steps": steps, "per_shape": rows}
 
 
 def run_ar_check(torch, dist, D, lib, dev, custom_ar, ar_link, rank, world):
@@ -738,6 +789,10 @@ def report(args, world, shapes, ms, total_ms, ms2, e2e_steps, launches, clocks, 
         for row in extra["fp4"]["per_shape"]:
             row["frac_hbm"] = round(row["gbs"] / peaks["hbm_gbs"], 3)
         line["fp4"] = extra["fp4"]
+    if "moe" in extra:
+        for row in extra["moe"]["per_shape"]:
+            row["frac_hbm"] = round(row["gbs"] / peaks["hbm_gbs"], 3)
+        line["moe"] = extra["moe"]
     if world == 1 and e2e_steps:
         b, s = cpu_sample(LAYERS, 16)
         line["cpu_baseline"] = {

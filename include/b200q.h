@@ -201,6 +201,34 @@ int b200q_marlin_gemm_fp4(const void* a, int64_t lda, const uint32_t* b_q_weight
                           b200q_stream_t stream);
 
 /*
+ * The mixture-of-experts form of the GEMM: moe_wna16_marlin_gemm of
+ * csrc/moe/marlin_moe_wna16/ops.cu:693-960 (torch schema csrc/moe/torch_bindings.cpp:62-73).
+ *   a                  [size_m, size_k] 16-bit activations (one row per token), row stride lda
+ *   b_q_weight         [num_experts][size_k/16, size_n*16/pack_factor] Marlin layout per expert
+ *   b_scales           [num_experts][num_groups, size_n] permuted as for b200q_marlin_gemm
+ *   b_zeros            [num_experts][num_groups, size_n/pack_factor] or null
+ *   b_bias             [num_experts][size_n] permuted, or null
+ *   c                  [size_m * top_k, size_n]: row id = token * top_k + slot
+ *   sorted_token_ids   [sorted_len] ids grouped by expert in blocks of moe_block_size, padded
+ *                      with values >= size_m * top_k (what moe_align_block_size returns)
+ *   expert_ids         [sorted_len / moe_block_size] expert of each block; -1 = skip (expert
+ *                      parallelism)
+ *   num_tokens_past_padded  device scalar: how many sorted ids are in use
+ *   topk_weights       [size_m * top_k] fp32; output rows are multiplied by it when
+ *                      mul_topk_weights != 0
+ * Rows of c whose id appears in no block are not written.  moe_block_size in {8, 16, 32, 48, 64};
+ * integer weight types (uint4b8, uint8b128, uint4, uint8), channel-wise or grouped scales; no
+ * act-order.  No scratch: a (block, column slice) is computed over the whole K by one CTA.
+ */
+int b200q_moe_wna16_marlin_gemm(
+    const void* a, int64_t lda, const uint32_t* b_q_weight, const void* b_scales,
+    const uint32_t* b_zeros, const void* b_bias, void* c, const int32_t* sorted_token_ids,
+    const int32_t* expert_ids, const int32_t* num_tokens_past_padded, const float* topk_weights,
+    int64_t sorted_len, int64_t moe_block_size, int64_t top_k, int mul_topk_weights,
+    int64_t num_experts, int64_t b_q_type_id, int a_dtype, int64_t size_m, int64_t size_n,
+    int64_t size_k, int64_t num_groups, b200q_stream_t stream);
+
+/*
  * b200q_marlin_gemm followed by the SUM all-reduce of C over the same peer link, as
  * RowParallelLinear does (vllm/model_executor/layers/linear.py:1386-1411: the
  * quantized matmul of the K shard, then tensor_model_parallel_all_reduce).  Where one

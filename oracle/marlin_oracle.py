@@ -476,6 +476,52 @@ def dequantize_fp4(codes: np.ndarray, scales: np.ndarray, group_size: int, dtype
     return round_to_dtype(w * round_to_dtype(scales.astype(np.float32), dtype)[g, :], dtype)
 
 
+# ---- mixture of experts ---------------------------------------------------------------------
+def moe_align_block_size(topk_ids: np.ndarray, block_size: int, num_experts: int):
+    """tests/kernels/moe/test_moe_align_block_size.py:92-170 (the golden torch implementation of
+    the reference's CUDA op): (token, slot) ids sorted by expert (stable), every expert's run
+    padded with `numel` to a multiple of block_size; the expert of every block (0 for blocks
+    past the end); the padded total."""
+    flat = topk_ids.reshape(-1)
+    numel = flat.size
+    max_padded = numel + num_experts * (block_size - 1)
+    sorted_ids = np.full(max_padded, numel, dtype=np.int32)
+    expert_ids = np.zeros(-(-max_padded // block_size), dtype=np.int32)
+    pos = blk = 0
+    for e in range(num_experts):
+        ids = np.nonzero(flat == e)[0]
+        if ids.size == 0:
+            continue
+        sorted_ids[pos:pos + ids.size] = ids
+        nb = -(-ids.size // block_size)
+        expert_ids[blk:blk + nb] = e
+        pos += nb * block_size
+        blk += nb
+    return sorted_ids, expert_ids, np.array([pos], dtype=np.int32)
+
+
+def moe_marlin_gemm_ref(a: np.ndarray, w_experts, sorted_ids: np.ndarray, expert_ids: np.ndarray,
+                        num_padded: int, topk_weights: np.ndarray | None, block_size: int,
+                        top_k: int, size_m: int, bias_experts=None) -> np.ndarray:
+    """moe_wna16_marlin_gemm as the kernel indexes it (marlin_moe_wna16/marlin_template.h:459-530,
+    920-930, 1500-1550): block b of `block_size` sorted ids uses expert expert_ids[b] (-1:
+    skipped); id < size_m * top_k reads row id // top_k of A and writes row id of the output
+    (times topk_weights[id] if given).  fp32; rows never written are NaN."""
+    n = w_experts[0].shape[1]
+    out = np.full((size_m * top_k, n), np.nan, dtype=np.float32)
+    for b in range(int(num_padded) // block_size):
+        e = int(expert_ids[b])
+        if e < 0:
+            continue
+        for i in sorted_ids[b * block_size:(b + 1) * block_size]:
+            if i < size_m * top_k:
+                v = a[i // top_k].astype(np.float32) @ w_experts[e].astype(np.float32)
+                if bias_experts is not None:
+                    v = v + bias_experts[e].astype(np.float32)
+                out[i] = v * (np.float32(topk_weights[i]) if topk_weights is not None else np.float32(1))
+    return out
+
+
 def gemm_ref(a: np.ndarray, w: np.ndarray, bias: np.ndarray | None = None) -> np.ndarray:
     """fp32-accumulated product of 16-bit operands held as float32."""
     out = a.astype(np.float32) @ w.astype(np.float32)

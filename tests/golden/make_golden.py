@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory from the reference's own
 Python packers (CPU only).
 
-Usage:  python tests/golden/make_golden.py <path-to-reference-checkout> [hqq|fp8|fp4|elementwise]
-        (with `hqq` / `fp8` / `fp4` / `elementwise` only that fixture is rewritten)
+Usage:  python tests/golden/make_golden.py <path-to-reference-checkout> [hqq|fp8|fp4|moe|elementwise]
+        (with `hqq` / `fp8` / `fp4` / `moe` / `elementwise` only that fixture is rewritten)
 
 The reference checkout is only needed to (re)generate the fixtures; the tests
 read the committed ``*.npz`` files and never import the reference.  All inputs
@@ -34,6 +34,9 @@ inputs):
                      (marlin_utils_fp4.py:304-397) run on CPU with the CUDA repack op replaced by
                      the CPU marlin_weights: the random codes, weight_ref, Marlin words, the
                      processed scale bytes, the processed global scale, and the product
+  moe_align.npz      torch_moe_align_block_size (the reference's golden torch implementation of its
+                     CUDA op, tests/kernels/moe/test_moe_align_block_size.py:92-170): routing tables,
+                     sorted ids, block experts, padded totals
   elementwise_{bf16,f16}.npz
                      the reference's torch implementations of the steps next to the
                      row-parallel GEMM: RMSNorm.forward_static with and without a residual
@@ -148,6 +151,31 @@ def make_fp4(here, mt) -> None:
             out_ref=(a.float() @ w_ref.float()).numpy())
 
 
+def make_moe_align(here, ref_root) -> None:
+    """Outputs of the reference's golden torch implementation of moe_align_block_size
+    (tests/kernels/moe/test_moe_align_block_size.py:92-170) for seeded routing tables."""
+    import importlib.util
+    import torch
+    spec = importlib.util.spec_from_file_location(
+        "ref_test_moe_align", os.path.join(ref_root, "tests/kernels/moe/test_moe_align_block_size.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    torch.manual_seed(17)
+    out = {}
+    for i, (m, topk, e, bs) in enumerate(((5, 2, 4, 16), (33, 4, 8, 8), (64, 2, 3, 64), (7, 1, 16, 32),
+                                          (128, 6, 32, 48))):
+        topk_ids = torch.stack([torch.randperm(e)[:topk] for _ in range(m)]).to(torch.int32)
+        if i == 2:
+            topk_ids[topk_ids == 1] = 0                                   # an expert without tokens
+        s, ex, n = mod.torch_moe_align_block_size(topk_ids, bs, e)
+        out[f"topk_ids_{i}"] = topk_ids.numpy()
+        out[f"cfg_{i}"] = np.array([m, topk, e, bs], dtype=np.int64)
+        out[f"sorted_{i}"] = s.numpy()
+        out[f"experts_{i}"] = ex.numpy()
+        out[f"num_{i}"] = n.numpy()
+    np.savez_compressed(os.path.join(here, "moe_align.npz"), cases=np.int64(5), **out)
+
+
 def make_elementwise(here) -> None:
     import torch
     from vllm.model_executor.layers.activation import SiluAndMul
@@ -185,6 +213,10 @@ def main(ref_root: str, only: str | None = None) -> None:
     if only == "fp8":
         make_fp8(here, mu, mt)
         print("fp8 fixtures written to", here)
+        return
+    if only == "moe":
+        make_moe_align(here, ref_root)
+        print("moe fixture written to", here)
         return
     if only == "fp4":
         make_fp4(here, mt)
@@ -283,6 +315,7 @@ def main(ref_root: str, only: str | None = None) -> None:
     make_hqq(here, mu, mt, qu)
     make_fp8(here, mu, mt)
     make_fp4(here, mt)
+    make_moe_align(here, ref_root)
     make_elementwise(here)
     print("golden fixtures written to", here)
 

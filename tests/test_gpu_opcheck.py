@@ -75,3 +75,25 @@ def test_cpp_checks_raise_like_the_reference(env):
         ns.gptq_marlin_gemm(*bad)
     with pytest.raises(RuntimeError, match="num_bits"):
         ns.gptq_marlin_repack(G.ti32(L.gptq_qweight), e, K, N, 5)
+
+
+def test_opcheck_moe_wna16_marlin_gemm():
+    import torch
+    from oracle import marlin_oracle as mo
+    from vllm_b200 import _custom_ops as ops
+    from vllm_b200 import marlin_utils as mu
+    from vllm_b200.scalar_type import scalar_types
+    dev = torch.device("cuda")
+    M, K, N, E, topk, bs = 6, 128, 64, 4, 2, 16
+    rng = np.random.default_rng(0)
+    topk_ids = np.stack([rng.permutation(E)[:topk] for _ in range(M)]).astype(np.int32)
+    sorted_ids, expert_ids, num = mo.moe_align_block_size(topk_ids, bs, E)
+    a = torch.randn((M, K), dtype=torch.float16, device=dev)
+    q = torch.randint(-2**31, 2**31 - 1, (E, K // 16, N * 2), dtype=torch.int32, device=dev)
+    s = torch.rand((E, 1, N), dtype=torch.float16, device=dev)
+    args = (a, None, q, None, s, None, None, None, None, mu.marlin_make_workspace_new(dev),
+            torch.from_numpy(sorted_ids).to(dev), torch.from_numpy(expert_ids).to(dev),
+            torch.from_numpy(num).to(dev), torch.ones(M * topk, device=dev), bs, topk, False, False,
+            scalar_types.uint4b8.id, M, N, K, True, False, True, False)
+    op = getattr(torch.ops, ops._MOE_NS).moe_wna16_marlin_gemm.default
+    torch.library.opcheck(op, args, test_utils=("test_schema", "test_autograd_registration", "test_faketensor"))

@@ -219,3 +219,17 @@ def test_fp4_scale_processing_matches_reference_bytes():
             s_perm = torch.from_numpy(mo.mxfp4_unprocess_scales(b)).to(td)
             got = f4.mxfp4_marlin_process_scales(s_perm).view(torch.uint8).numpy()
         assert np.array_equal(got, b), name
+
+
+def test_moe_align_block_size_torch_matches_reference_golden():
+    """This package's device-side moe_align_block_size (torch ops, here on CPU tensors) against the
+    outputs of the reference's golden implementation."""
+    import os
+    from vllm_b200 import fused_moe
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "moe_align.npz"))
+    for i in range(int(g["cases"])):
+        m, topk, e, bs = (int(x) for x in g[f"cfg_{i}"])
+        s, ex, n = fused_moe.moe_align_block_size(torch.from_numpy(g[f"topk_ids_{i}"]), bs, e)
+        assert int(n[0]) == int(g[f"num_{i}"].reshape(-1)[0]), i
+        assert np.array_equal(s.numpy(), g[f"sorted_{i}"]), i
+        assert np.array_equal(ex.numpy(), g[f"experts_{i}"]), i

@@ -211,3 +211,14 @@ def test_fp4_decode_table():
     c = np.arange(16, dtype=np.uint8)
     want = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0]
     assert mo.fp4_e2m1_decode(c).tolist() == want
+
+
+def test_moe_align_block_size_matches_reference():
+    """The oracle's moe_align_block_size against the reference's golden torch implementation."""
+    g = _load("moe_align.npz")
+    for i in range(int(g["cases"])):
+        m, topk, e, bs = (int(x) for x in g[f"cfg_{i}"])
+        s, ex, n = mo.moe_align_block_size(g[f"topk_ids_{i}"], bs, e)
+        assert int(n[0]) == int(g[f"num_{i}"].reshape(-1)[0]), i
+        assert np.array_equal(s, g[f"sorted_{i}"]), i
+        assert np.array_equal(ex, g[f"experts_{i}"]), i

@@ -42,6 +42,18 @@ def _pick_namespace() -> str:
 _NS = _pick_namespace()
 
 
+def _pick_moe_namespace() -> str:
+    """The reference keeps its mixture-of-experts operators in `_moe_C`."""
+    try:
+        torch.ops._moe_C.moe_wna16_marlin_gemm  # noqa: B018 - defined by someone else?
+        return "b200q_moe"
+    except (AttributeError, RuntimeError):
+        return "_moe_C" if _NS == "_C" else "b200q_moe"
+
+
+_MOE_NS = _pick_moe_namespace()
+
+
 def _load_torch_extension(ns: str) -> None:
     path = os.path.join(os.path.dirname(_lib.LIB_PATH), "b200q_torch.so")
     if not os.path.exists(path):
@@ -58,6 +70,8 @@ def _load_torch_extension(ns: str) -> None:
     if rc != 0:
         raise _lib.B200QError(f"operator names in torch.ops.{ns} are taken by another extension; "
                               "set VLLM_B200_OPS_NAMESPACE to a free namespace")
+    if ext.b200q_torch_register_moe(_MOE_NS.encode()) != 0:
+        raise _lib.B200QError(f"torch.ops.{_MOE_NS}.moe_wna16_marlin_gemm is taken by another extension")
 
 
 _load_torch_extension(_NS)
@@ -137,7 +151,17 @@ def _permute_cols_fake(A, perm):
     return torch.empty((A.size(0), A.size(1)), dtype=A.dtype, device=A.device)
 
 
+@torch.library.register_fake(f"{_MOE_NS}::moe_wna16_marlin_gemm")
+def _moe_wna16_marlin_gemm_fake(a, c_or_none, b_q_weight, b_bias_or_none, b_scales, global_scale,
+                                b_zeros_or_none, g_idx_or_none, perm_or_none, workspace,
+                                sorted_token_ids, expert_ids, num_tokens_past_padded, topk_weights,
+                                moe_block_size, top_k, mul_topk_weights, is_ep, b_q_type_id, size_m,
+                                size_n, size_k, is_full_k, use_atomic_add, use_fp32_reduce, is_zp_float):
+    return torch.empty((size_m * top_k, size_n), dtype=a.dtype, device=a.device)
+
+
 _ops = getattr(torch.ops, _NS)
+_moe_ops = getattr(torch.ops, _MOE_NS)
 
 # ---------------------------------------------------------------------------
 # Python wrappers with the reference's signatures
@@ -196,6 +220,26 @@ def gptq_marlin_gemm(a: torch.Tensor, c: torch.Tensor | None, b_q_weight: torch.
     return _ops.gptq_marlin_gemm(a, c, b_q_weight, b_bias, b_scales, global_scale, b_zeros, g_idx,
                                  perm, workspace, b_q_type.id, size_m, size_n, size_k, is_k_full,
                                  use_atomic_add, use_fp32_reduce, is_zp_float)
+
+
+def moe_wna16_marlin_gemm(input: torch.Tensor, output: torch.Tensor | None, b_qweight: torch.Tensor,
+                          b_bias: torch.Tensor | None, b_scales: torch.Tensor,
+                          global_scale: torch.Tensor | None, b_qzeros: torch.Tensor | None,
+                          g_idx: torch.Tensor | None, perm: torch.Tensor | None,
+                          workspace: torch.Tensor, sorted_token_ids: torch.Tensor,
+                          expert_ids: torch.Tensor, num_tokens_past_padded: torch.Tensor,
+                          topk_weights: torch.Tensor, moe_block_size: int, top_k: int,
+                          mul_topk_weights: bool, is_ep: bool, b_q_type: ScalarType, size_m: int,
+                          size_n: int, size_k: int, is_k_full: bool = True,
+                          use_atomic_add: bool = False, use_fp32_reduce: bool = True,
+                          is_zp_float: bool = False) -> torch.Tensor:
+    """vllm/_custom_ops.py:1907-1963: the Marlin GEMM over blocks of tokens sorted by expert;
+    returns [size_m * top_k, size_n]."""
+    return _moe_ops.moe_wna16_marlin_gemm(
+        input, output, b_qweight, b_bias, b_scales, global_scale, b_qzeros, g_idx, perm, workspace,
+        sorted_token_ids, expert_ids, num_tokens_past_padded, topk_weights, moe_block_size, top_k,
+        mul_topk_weights, is_ep, b_q_type.id, size_m, size_n, size_k, is_k_full, use_atomic_add,
+        use_fp32_reduce, is_zp_float)
 
 
 def _dtype_code(t: torch.Tensor) -> int:

@@ -25,6 +25,7 @@ EXPORTS = (
     "b200q_marlin_gemm_preferred_scratch_bytes",
     "b200q_marlin_gemm",
     "b200q_marlin_gemm_fp4",
+    "b200q_moe_wna16_marlin_gemm",
     "b200q_marlin_gemm_noalloc_max_scratch",
     "b200q_marlin_gemm_noalloc",
     "b200q_all_reduce_state_bytes",
@@ -88,6 +89,10 @@ def load() -> ctypes.CDLL:
     lib.b200q_marlin_gemm_fp4.restype = i32
     lib.b200q_marlin_gemm_fp4.argtypes = [
         vp, i64, vp, vp, vp, i32, vp, vp, vp, c.c_size_t, vp, i64, i32, i64, i64, i64, i64, vp]
+    lib.b200q_moe_wna16_marlin_gemm.restype = i32
+    lib.b200q_moe_wna16_marlin_gemm.argtypes = [
+        vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i64, i64, i32, i64, i64,
+        i64, i64, vp]
     lib.b200q_marlin_gemm_all_reduce.restype = i32
     lib.b200q_marlin_gemm_all_reduce.argtypes = [
         vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, c.c_size_t, vp, i64, i64, i32,

@@ -332,7 +332,7 @@ static int gemm_impl(const void* a, int64_t lda, const uint32_t* b_q_weight, con
       if (gm == kChannel && mb <= 4) ntw = 2;
       if (gm == kGrouped && mb <= 2) ntw = 2;
     }
-    StreamParams p;
+    StreamParams p = {};
     p.a = static_cast<const char*>(a_used) + (size_t)m0 * lda_used * 2;
     p.lda = lda_used;
     p.b = b_q_weight;
@@ -384,6 +384,88 @@ extern "C" int b200q_marlin_gemm(const void* a, int64_t lda, const uint32_t* b_q
   return gemm_impl(a, lda, b_q_weight, b_scales, b_zeros, g_idx, perm, b_bias, c, scratch,
                    scratch_bytes, workspace, workspace_len, b_q_type_id, a_dtype, size_m, size_n,
                    size_k, num_groups, flags, static_cast<cudaStream_t>(stream), nullptr);
+}
+
+// Mixture-of-experts GEMM: see include/b200q.h
+extern "C" int b200q_moe_wna16_marlin_gemm(
+    const void* a, int64_t lda, const uint32_t* b_q_weight, const void* b_scales,
+    const uint32_t* b_zeros, const void* b_bias, void* c, const int32_t* sorted_token_ids,
+    const int32_t* expert_ids, const int32_t* num_tokens_past_padded, const float* topk_weights,
+    int64_t sorted_len, int64_t moe_block_size, int64_t top_k, int mul_topk_weights,
+    int64_t num_experts, int64_t b_q_type_id, int a_dtype, int64_t size_m, int64_t size_n,
+    int64_t size_k, int64_t num_groups, b200q_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int bits = 0;
+  bool type_has_zp = false;
+  if (b_q_type_id == kTypeU4B8) { bits = 4; }
+  else if (b_q_type_id == kTypeU8B128) { bits = 8; }
+  else if (b_q_type_id == kTypeU4) { bits = 4; type_has_zp = true; }
+  else if (b_q_type_id == kTypeU8) { bits = 8; type_has_zp = true; }
+  else {
+    set_error("moe: b_q_type id %lld is not supported (uint4b8, uint8b128, uint4, uint8)",
+              (long long)b_q_type_id);
+    return B200Q_EUNSUPPORTED;
+  }
+  const bool has_zp = b_zeros != nullptr;
+  B200Q_REQUIRE(has_zp == type_has_zp, B200Q_EINVAL,
+                "b_q_type must be u4 or u8 with zero-points, uint4b8 or uint8b128 without");
+  B200Q_REQUIRE(a_dtype == B200Q_F16 || a_dtype == B200Q_BF16, B200Q_EINVAL,
+                "moe_wna16_marlin_gemm only supports bfloat16 and float16");
+  // ops.cu:709-713
+  B200Q_REQUIRE(moe_block_size == 8 || (moe_block_size % 16 == 0 && moe_block_size >= 16 &&
+                                        moe_block_size <= 64),
+                B200Q_EINVAL, "unsupported moe_block_size=%lld", (long long)moe_block_size);
+  B200Q_REQUIRE(size_k % 16 == 0 && size_n % 64 == 0 && size_n > 0 && size_k > 0, B200Q_EINVAL,
+                "Invalid MNK = [%lld, %lld, %lld]", (long long)size_m, (long long)size_n, (long long)size_k);
+  B200Q_REQUIRE(top_k >= 1 && num_experts >= 1 && num_groups >= 1 && size_m >= 0, B200Q_EINVAL,
+                "invalid top_k / num_experts / num_groups");
+  if (size_m == 0 || sorted_len == 0) return B200Q_OK;
+  B200Q_REQUIRE(a && b_q_weight && b_scales && c && sorted_token_ids && expert_ids &&
+                    num_tokens_past_padded, B200Q_EINVAL, "null tensor pointer");
+  B200Q_REQUIRE(!mul_topk_weights || topk_weights, B200Q_EINVAL, "mul_topk_weights without topk_weights");
+  B200Q_REQUIRE(lda >= size_k && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0,
+                B200Q_EINVAL, "A must be aligned to 16 bytes with a row stride divisible by 8");
+  B200Q_REQUIRE(size_k % num_groups == 0, B200Q_EINVAL, "size_k = %lld, is not divisible by num_groups = %lld",
+                (long long)size_k, (long long)num_groups);
+  const int kt_total = (int)(size_k / 16);
+  int gm = kChannel, group_blocks = kt_total;
+  if (num_groups > 1) {
+    const int64_t group_size = size_k / num_groups;
+    B200Q_REQUIRE(group_size % 16 == 0, B200Q_EUNSUPPORTED, "group_size = %lld is not a multiple of 16",
+                  (long long)group_size);
+    gm = kGrouped;
+    group_blocks = (int)(group_size / 16);
+  }
+  StreamParams p = {};
+  p.a = a; p.lda = lda; p.b = b_q_weight; p.scales = b_scales; p.zeros = b_zeros; p.bias = b_bias;
+  p.c = c;
+  p.m = (int)moe_block_size; p.n = (int)size_n; p.k = (int)size_k;
+  p.kt_total = kt_total;
+  p.slices = (int)(size_n / 64);
+  p.group_blocks = group_blocks;
+  p.num_groups = (int)num_groups;
+  p.moe_sorted_ids = sorted_token_ids;
+  p.moe_expert_ids = expert_ids;
+  p.moe_num_padded = num_tokens_past_padded;
+  p.moe_topk_weights = mul_topk_weights ? topk_weights : nullptr;
+  p.moe_blocks = (int)(sorted_len / moe_block_size);
+  p.moe_rows = (int)(size_m * top_k);
+  p.moe_top_k = (int)top_k;
+  p.moe_b_stride = (long long)kt_total * size_n * 16 * bits / 32;      // words per expert
+  p.moe_s_stride = (long long)num_groups * size_n;
+  p.moe_z_stride = (long long)num_groups * size_n * bits / 32;
+  p.moe_bias_stride = size_n;
+  if (p.moe_blocks == 0) return B200Q_OK;
+  const int mb8 = (int)(moe_block_size / 8);  // 8-row blocks: 2, 4, 6, 8
+  int rc;
+  if (a_dtype == B200Q_F16)
+    rc = bits == 4 ? dispatch_stream<half, 4>(p, has_zp, gm, mb8, 1, 1 << 20, stream)
+                   : dispatch_stream<half, 8>(p, has_zp, gm, mb8, 1, 1 << 20, stream);
+  else
+    rc = bits == 4 ? dispatch_stream<__nv_bfloat16, 4>(p, has_zp, gm, mb8, 1, 1 << 20, stream)
+                   : dispatch_stream<__nv_bfloat16, 8>(p, has_zp, gm, mb8, 1, 1 << 20, stream);
+  if (rc == B200Q_EUNSUPPORTED && g_error[0] == 0) set_error("moe: unsupported configuration");
+  return rc;
 }
 
 extern "C" int b200q_marlin_gemm_fp4(const void* a, int64_t lda, const uint32_t* b_q_weight,

@@ -49,9 +49,15 @@ struct LookupCfg {
 // scale, applied to the fp32 sums, carries the two corrections (dequant.h:398-414, 470-499,
 // marlin_template.h:1180-1188, 1500-1502).  MXFP4 (2): the weights are re-biased exactly and the
 // scale bytes are bf16 exponent fields (dequant.h:452-468, 501-513).
+// MOE: the mixture-of-experts form (csrc/moe/marlin_moe_wna16/marlin_template.h:374-530, 585-590,
+// 920-930, 1500-1550): the rows of A are gathered through blocks of p.m sorted ids
+// (row = id / top_k, ids >= moe_rows are padding), block b multiplies with the weights of expert
+// expert_ids[b] (-1: skipped), output row = id, optionally scaled by topk_weights[id].  A work
+// unit is (block, column slice) over the whole K: no partial sums cross CTAs.
 template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, int MINB, bool ZPF = false,
-          bool FP8 = false, bool FP4 = false>
+          bool FP8 = false, bool FP4 = false, bool MOE = false>
 __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const StreamParams p) {
+  static_assert(!MOE || (!ZPF && !FP8 && !FP4 && GM != kLookup), "moe: integer weight types");
   static_assert(!FP4 || (BITS == 4 && !HAS_ZP && GM == kGrouped && !FP8), "fp4 weights: grouped scales");
   static_assert(!ZPF || (HAS_ZP && GM == kGrouped), "float zero-points come with grouped scales");
   static_assert(!FP8 || (BITS == 8 && !HAS_ZP && GM != kLookup), "fp8 weights: 8 bits, no zero-points");
@@ -67,10 +73,16 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
   const int NT = p.n / 64;
   const uint16_t* __restrict__ A = static_cast<const uint16_t*>(p.a);
   const uint16_t* __restrict__ S = static_cast<const uint16_t*>(p.scales);
+  const uint4* __restrict__ Bw = reinterpret_cast<const uint4*>(p.b);
+  const uint32_t* __restrict__ Zp = p.zeros;
+  const uint16_t* __restrict__ Bias = static_cast<const uint16_t*>(p.bias);
 
-  const long long total = (long long)p.slices * KT;
-  const long long u_begin = total * blockIdx.x / gridDim.x;
-  const long long u_end = total * (blockIdx.x + 1) / gridDim.x;
+  const long long n_slices = MOE ? (long long)p.moe_blocks * p.slices : p.slices;
+  const long long total = n_slices * KT;
+  // moe: whole (block, slice) units per CTA
+  const long long u_begin = MOE ? n_slices * blockIdx.x / gridDim.x * KT : total * blockIdx.x / gridDim.x;
+  const long long u_end = MOE ? n_slices * (blockIdx.x + 1) / gridDim.x * KT
+                              : total * (blockIdx.x + 1) / gridDim.x;
 
   const uint32_t ring = smem_u32(smem) + warp * (D * Cfg::kStageBytes);
   float* red = reinterpret_cast<float*>(smem);
@@ -81,7 +93,26 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
     const int kt0 = (int)(u % KT);
     const int kt1 = (int)min((long long)KT, kt0 + (u_end - u));
     u += kt1 - kt0;
-    const int nt0 = slice * NTW;  // first 64-column tile of the slice
+    int moe_block = 0;
+    int a_row[MB];   // moe: source row of A for each 16-row block's row this lane stages, -1 = none
+    (void)a_row;
+    if (MOE) {
+      moe_block = slice / p.slices;
+      if (moe_block * p.m >= *p.moe_num_padded) continue;
+      const int expert = p.moe_expert_ids[moe_block];
+      if (expert < 0) continue;
+      Bw = reinterpret_cast<const uint4*>(p.b + (size_t)expert * p.moe_b_stride);
+      S = static_cast<const uint16_t*>(p.scales) + (size_t)expert * p.moe_s_stride;
+      if (HAS_ZP) Zp = p.zeros + (size_t)expert * p.moe_z_stride;
+      if (p.bias) Bias = static_cast<const uint16_t*>(p.bias) + (size_t)expert * p.moe_bias_stride;
+#pragma unroll
+      for (int i = 0; i < MB; ++i) {
+        const int row = i * 16 + (lane >> 1);
+        const int id = row < p.m ? p.moe_sorted_ids[moe_block * p.m + row] : p.moe_rows;
+        a_row[i] = id < p.moe_rows ? id / p.moe_top_k : -1;
+      }
+    }
+    const int nt0 = (MOE ? slice % p.slices : slice) * NTW;  // first 64-column tile of the slice
 
     // this warp's contiguous share of [kt0, kt1)
     const int len = kt1 - kt0;
@@ -107,8 +138,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
     auto issue = [&](int kt, int stage) {
       const uint32_t st = ring + stage * Cfg::kStageBytes;
       if (kt < we) {
-        const uint4* wsrc =
-            reinterpret_cast<const uint4*>(p.b) + ((size_t)kt * NT + nt0) * (Cfg::kTileBytes / 16);
+        const uint4* wsrc = Bw + ((size_t)kt * NT + nt0) * (Cfg::kTileBytes / 16);
 #pragma unroll
         for (int j = 0; j < NTW; ++j) {
           if (BITS == 4) {
@@ -128,8 +158,8 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
           const int pos = 2 * r + (h ^ ((r >> 2) & 1));
 #pragma unroll
           for (int i = 0; i < MB; ++i) {
-            const int row = i * 16 + r;
-            const bool ok = row < p.m;
+            const int row = MOE ? a_row[i] : i * 16 + r;
+            const bool ok = MOE ? row >= 0 : row < p.m;
             const uint16_t* src = A + (size_t)(ok ? row : 0) * p.lda + kt * 16 + h * 8;
             cp_async16(st + Cfg::kAOff + i * 512 + pos * 16, src, ok ? 16 : 0);
           }
@@ -147,7 +177,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
             constexpr int kChunks = NTW * 8 * BITS / 16;  // 16 B chunks of zero-point words
             if (lane < kChunks)
               cp_async16(st + Cfg::kZOff + lane * 16,
-                         p.zeros + (size_t)g * (p.n * BITS / 32) + nt0 * (2 * BITS) + lane * 4);
+                         Zp + (size_t)g * (p.n * BITS / 32) + nt0 * (2 * BITS) + lane * 4);
           }
         }
       }
@@ -350,7 +380,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
     const long long s_first_u = (long long)slice * KT;
     const int first_cta = (int)(((s_first_u + 1) * gridDim.x - 1) / total);
     const int last_cta = (int)(((s_first_u + KT) * gridDim.x - 1) / total);
-    const bool split = first_cta != last_cta;
+    const bool split = !MOE && first_cta != last_cta;
 
     float outv[MB][Cfg::kEpt];
     const int o_row = threadIdx.x >> 4;                // 0..15
@@ -434,20 +464,27 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
         cs[e] = (GM == kChannel) ? Pair<T>::to_float(S[single_perm_pos(n_base + e)]) : 1.f;
         if (FP8 && GM == kChannel) cs[e] *= Fp8Cvt<T>::kRebiasInv;
         if (FP4 && p.w_fp4 == 1) cs[e] = Pair<T>::to_float(*static_cast<const uint16_t*>(p.global_scale));
-        bs[e] = p.bias ? Pair<T>::to_float(
-                             static_cast<const uint16_t*>(p.bias)[single_perm_pos(n_base + e)])
-                       : 0.f;
+        bs[e] = p.bias ? Pair<T>::to_float(Bias[single_perm_pos(n_base + e)]) : 0.f;
       }
       uint16_t* C = static_cast<uint16_t*>(p.c);
 #pragma unroll
       for (int i = 0; i < MB; ++i) {
-        const int row = i * 16 + o_row;
-        if (row < p.m) {
+        int row = i * 16 + o_row;
+        bool live = row < p.m;
+        float tw = 1.f;
+        if (MOE) {
+          // output row = the sorted id itself; padding ids write nothing
+          const int id = live ? p.moe_sorted_ids[moe_block * p.m + row] : p.moe_rows;
+          live = id < p.moe_rows;
+          row = id;
+          if (live && p.moe_topk_weights) tw = p.moe_topk_weights[id];
+        }
+        if (live) {
           uint32_t packed[Cfg::kEpt / 2];
 #pragma unroll
           for (int e = 0; e < Cfg::kEpt; e += 2) {
-            const float v0 = outv[i][e] * cs[e] + bs[e];
-            const float v1 = outv[i][e + 1] * cs[e + 1] + bs[e + 1];
+            const float v0 = (outv[i][e] * cs[e] + bs[e]) * tw;
+            const float v1 = (outv[i][e + 1] * cs[e + 1] + bs[e + 1]) * tw;
             packed[e / 2] = (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
           }
           uint16_t* dst = C + (size_t)row * p.n + n_base;
@@ -464,11 +501,11 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_lookup_kernel(const
 
 // Host launcher for one (type, bits, zp, group mode, MB, NTW) variant.
 template <typename T, int BITS, bool HAS_ZP, int GM, int MB, int NTW, bool ZPF = false, bool FP8 = false,
-          bool FP4 = false>
+          bool FP4 = false, bool MOE = false>
 int launch_lookup(const StreamParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = LookupCfg<BITS, HAS_ZP, GM, MB, NTW, ZPF>;
   constexpr int kMinBlocks = (MB * NTW <= 2 && Cfg::kSmemBytes <= 112 * 1024) ? 2 : 1;
-  auto kernel = gemm_lookup_kernel<T, BITS, HAS_ZP, GM, MB, NTW, kMinBlocks, ZPF, FP8, FP4>;
+  auto kernel = gemm_lookup_kernel<T, BITS, HAS_ZP, GM, MB, NTW, kMinBlocks, ZPF, FP8, FP4, MOE>;
   static bool attr_done[64] = {};  // per device; benign race: the call is idempotent
   int dev = 0;
   B200Q_CUDA_OK(cudaGetDevice(&dev));
@@ -477,8 +514,8 @@ int launch_lookup(const StreamParams& p, int max_ctas, cudaStream_t stream) {
                                        Cfg::kSmemBytes));
     attr_done[dev & 63] = true;
   }
-  const long long total = (long long)p.slices * p.kt_total;
-  long long want = (long long)device_sm_count() * kMinBlocks;
+  const long long total = (long long)p.slices * p.kt_total * (MOE ? p.moe_blocks : 1);
+  long long want = (long long)device_sm_count() * kMinBlocks * (MOE ? 4 : 1);  // moe: many blocks are empty
   if (want > max_ctas) want = max_ctas;
   const long long by_work = (total + 15) / 16;  // at least 16 k-tiles per CTA
   int grid = (int)(want < by_work ? want : by_work);

@@ -102,6 +102,30 @@ int fp4_weights(const StreamParams& p, int gm, int rows8, int ntw, int max_ctas,
   return B200Q_EUNSUPPORTED;
 }
 
+// mixture-of-experts form: the reference-order kernel over (block of sorted ids, column slice)
+template <bool HAS_ZP, int GM>
+int moe_blocks(const StreamParams& p, int rows8, int max_ctas, cudaStream_t stream) {
+  const int mb = (rows8 + 1) / 2;  // 16-row blocks
+  switch (mb) {
+    case 1: return launch_lookup<T, B, HAS_ZP, GM, 1, 1, false, false, false, true>(p, max_ctas, stream);
+    case 2: return launch_lookup<T, B, HAS_ZP, GM, 2, 1, false, false, false, true>(p, max_ctas, stream);
+    case 3:
+    case 4: return launch_lookup<T, B, HAS_ZP, GM, 4, 1, false, false, false, true>(p, max_ctas, stream);
+  }
+  return B200Q_EUNSUPPORTED;
+}
+
+int moe(const StreamParams& p, bool has_zp, int gm, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
+  if (ntw != 1 || p.zp_float) return B200Q_EUNSUPPORTED;
+  if (gm == kChannel)
+    return has_zp ? moe_blocks<true, kChannel>(p, rows8, max_ctas, stream)
+                  : moe_blocks<false, kChannel>(p, rows8, max_ctas, stream);
+  if (gm == kGrouped)
+    return has_zp ? moe_blocks<true, kGrouped>(p, rows8, max_ctas, stream)
+                  : moe_blocks<false, kGrouped>(p, rows8, max_ctas, stream);
+  return B200Q_EUNSUPPORTED;
+}
+
 int lookup(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t stream) {
   if (ntw != 1) return B200Q_EUNSUPPORTED;
   const int mb = (rows8 + 1) / 2;  // 16-row blocks
@@ -118,6 +142,7 @@ int lookup(const StreamParams& p, int rows8, int ntw, int max_ctas, cudaStream_t
 template <>
 int dispatch_stream<InstT, INST_BITS>(const StreamParams& p, bool has_zp, int gm, int mb, int ntw,
                                       int max_ctas, cudaStream_t stream) {
+  if (p.moe_sorted_ids) return (p.w_fp8 || p.w_fp4) ? B200Q_EUNSUPPORTED : moe(p, has_zp, gm, mb, ntw, max_ctas, stream);
   if (p.w_fp8) return has_zp ? B200Q_EUNSUPPORTED : fp8_weights(p, gm, mb, ntw, max_ctas, stream);
   if (p.w_fp4) return has_zp ? B200Q_EUNSUPPORTED : fp4_weights(p, gm, mb, ntw, max_ctas, stream);
   if (p.zp_float)

@@ -392,6 +392,107 @@ std::unique_ptr<torch::Library> g_defs, g_impls;
 // Define the operators in namespace `ns` and register the CUDA implementations.  Returns 0,
 // or -1 when the definitions clash with operators that already exist there (nothing is then
 // registered by this call that was not registered before the clash).
+// moe_wna16_marlin_gemm, csrc/moe/marlin_moe_wna16/ops.cu:693-960
+at::Tensor moe_wna16_marlin_gemm(
+    at::Tensor& a, std::optional<at::Tensor> const& c_or_none, at::Tensor& b_q_weight,
+    std::optional<at::Tensor> const& b_bias_or_none, at::Tensor& b_scales,
+    std::optional<at::Tensor> const& global_scale_or_none,
+    std::optional<at::Tensor> const& b_zeros_or_none, std::optional<at::Tensor> const& g_idx_or_none,
+    std::optional<at::Tensor> const& perm_or_none, at::Tensor& workspace,
+    at::Tensor& sorted_token_ids, at::Tensor& expert_ids, at::Tensor& num_tokens_past_padded,
+    at::Tensor& topk_weights, int64_t moe_block_size, int64_t top_k, bool mul_topk_weights,
+    bool is_ep, int64_t b_q_type_id, int64_t size_m, int64_t size_n, int64_t size_k, bool is_k_full,
+    bool use_atomic_add, bool use_fp32_reduce, bool is_zp_float) {
+  (void)workspace; (void)is_ep; (void)is_k_full; (void)use_atomic_add; (void)use_fp32_reduce;
+  TypeInfo qt;
+  TORCH_CHECK(decode_type(b_q_type_id, &qt) && !qt.is_float,
+              "moe_wna16_marlin_gemm: b_q_type must be uint4b8, uint8b128, uint4 or uint8; id ",
+              b_q_type_id, " is not supported");
+  const int pf = 32 / qt.bits;
+  TORCH_CHECK(moe_block_size == 8 ||
+                  (moe_block_size % 16 == 0 && moe_block_size >= 16 && moe_block_size <= 64),
+              "unsupported moe_block_size=", moe_block_size);
+  TORCH_CHECK(a.dim() == 2 && a.size(0) == size_m && a.size(1) == size_k,
+              "Shape mismatch: a = [", a.size(0), ", ", a.size(1), "], size_m = ", size_m,
+              ", size_k = ", size_k);
+  TORCH_CHECK(a.is_cuda() && a.stride(1) == 1 && a.stride(0) % 8 == 0, "A must be a CUDA tensor ",
+              "with unit inner stride and a row stride divisible by 8");
+  TORCH_CHECK(a.scalar_type() == at::kHalf || a.scalar_type() == at::kBFloat16,
+              "moe_wna16_marlin_gemm only supports bfloat16 and float16");
+  TORCH_CHECK(b_q_weight.is_cuda() && b_q_weight.is_contiguous() && b_q_weight.dim() == 3,
+              "b_q_weight must be a contiguous CUDA tensor [experts, size_k / 16, size_n * 16 / pack_factor]");
+  const int64_t num_experts = b_q_weight.size(0);
+  TORCH_CHECK(size_k % 16 == 0 && b_q_weight.size(1) == size_k / 16,
+              "Shape mismatch: b_q_weight.size(1) = ", b_q_weight.size(1), ", size_k = ", size_k);
+  TORCH_CHECK(b_q_weight.size(2) % 16 == 0 && b_q_weight.size(2) / 16 * pf == size_n,
+              "size_n = ", size_n, ", actual_size_n = ", b_q_weight.size(2) / 16 * pf);
+  TORCH_CHECK(b_scales.is_cuda() && b_scales.is_contiguous() && b_scales.dim() == 3 &&
+                  b_scales.size(0) == num_experts && b_scales.size(2) == size_n &&
+                  b_scales.scalar_type() == a.scalar_type(),
+              "b_scales must be [experts, groups, size_n] of the dtype of a");
+  const int64_t num_groups = b_scales.size(1);
+  TORCH_CHECK(!global_scale_or_none.has_value(), "global_scale can only be used for nvfp4 format.");
+  TORCH_CHECK(!is_zp_float, "moe_wna16_marlin_gemm: float zero-points are not supported");
+  bool act_order = false;
+  if (g_idx_or_none.has_value() && perm_or_none.has_value())
+    act_order = g_idx_or_none.value().size(-1) > 0 || perm_or_none.value().size(-1) > 0;
+  TORCH_CHECK(!act_order, "moe_wna16_marlin_gemm: act_order is not supported");
+  const uint32_t* zeros = nullptr;
+  if (b_zeros_or_none.has_value() && b_zeros_or_none.value().size(-1) > 0) {
+    const at::Tensor& z = b_zeros_or_none.value();
+    TORCH_CHECK(z.is_cuda() && z.is_contiguous() && z.dim() == 3, "b_zeros rank = ", z.dim(), " is not 3");
+    TORCH_CHECK(z.size(0) == num_experts && z.size(1) == num_groups && z.size(2) == size_n / pf &&
+                    z.scalar_type() == at::kInt,
+                "b_zeros must be int32 [experts, groups, size_n / pack_factor]");
+    zeros = static_cast<const uint32_t*>(z.data_ptr());
+  }
+  const void* bias = nullptr;
+  if (b_bias_or_none.has_value()) {
+    const at::Tensor& b = b_bias_or_none.value();
+    TORCH_CHECK(b.is_cuda() && b.is_contiguous() && b.numel() == num_experts * size_n &&
+                    b.scalar_type() == a.scalar_type(),
+                "b_bias must be [experts, size_n] of the dtype of a");
+    bias = b.data_ptr();
+  }
+  TORCH_CHECK(sorted_token_ids.is_cuda() && sorted_token_ids.is_contiguous() &&
+                  sorted_token_ids.scalar_type() == at::kInt,
+              "sorted_token_ids must be a contiguous int32 CUDA tensor");
+  TORCH_CHECK(expert_ids.is_cuda() && expert_ids.is_contiguous() && expert_ids.scalar_type() == at::kInt,
+              "expert_ids must be a contiguous int32 CUDA tensor");
+  TORCH_CHECK(num_tokens_past_padded.is_cuda() && num_tokens_past_padded.scalar_type() == at::kInt &&
+                  num_tokens_past_padded.numel() >= 1,
+              "num_tokens_past_padded must be an int32 CUDA tensor");
+  const int64_t sorted_len = sorted_token_ids.numel() / moe_block_size * moe_block_size;
+  TORCH_CHECK(expert_ids.numel() >= sorted_len / moe_block_size, "expert_ids has ", expert_ids.numel(),
+              " entries for ", sorted_len / moe_block_size, " blocks");
+  TORCH_CHECK(topk_weights.is_cuda() && topk_weights.scalar_type() == at::kFloat &&
+                  topk_weights.is_contiguous() && (!mul_topk_weights || topk_weights.numel() >= size_m * top_k),
+              "topk_weights must be a contiguous float32 CUDA tensor of size_m * top_k values");
+  at::Tensor c;
+  if (c_or_none.has_value()) {
+    c = c_or_none.value();
+    TORCH_CHECK(c.is_cuda() && c.is_contiguous() && c.size(0) == size_m * top_k && c.size(1) == size_n &&
+                    c.scalar_type() == a.scalar_type(),
+                "c must be [size_m * top_k, size_n] of the dtype of a");
+  } else {
+    c = at::empty({size_m * top_k, size_n}, a.options());
+  }
+  if (size_m == 0) return c;
+  const c10::cuda::OptionalCUDAGuard guard(device_of(a));
+  const cudaStream_t stream = at::cuda::getCurrentCUDAStream(a.get_device());
+  const int rc = b200q_moe_wna16_marlin_gemm(
+      a.data_ptr(), a.stride(0), static_cast<const uint32_t*>(b_q_weight.data_ptr()),
+      b_scales.data_ptr(), zeros, bias, c.data_ptr(), sorted_token_ids.data_ptr<int32_t>(),
+      expert_ids.data_ptr<int32_t>(), num_tokens_past_padded.data_ptr<int32_t>(),
+      topk_weights.data_ptr<float>(), sorted_len, moe_block_size, top_k, mul_topk_weights ? 1 : 0,
+      num_experts, b_q_type_id, a.scalar_type() == at::kBFloat16 ? B200Q_BF16 : B200Q_F16, size_m,
+      size_n, size_k, num_groups, stream);
+  B200Q_TORCH_OK(rc, "moe_wna16_marlin_gemm");
+  return c;
+}
+
+std::unique_ptr<torch::Library> g_moe_defs, g_moe_impls;
+
 extern "C" int b200q_torch_register(const char* ns) {
   if (g_defs) return 0;
   try {
@@ -432,6 +533,38 @@ extern "C" int b200q_torch_register(const char* ns) {
   } catch (const std::exception&) {
     g_impls.reset();
     g_defs.reset();
+    return -1;
+  }
+  return 0;
+}
+
+// The mixture-of-experts operator lives in its own namespace in the reference (`_moe_C`,
+// csrc/moe/torch_bindings.cpp:62-73).
+extern "C" int b200q_torch_register_moe(const char* ns) {
+  if (g_moe_defs) return 0;
+  try {
+    const std::string name(ns);
+    g_moe_defs = std::make_unique<torch::Library>(torch::Library::FRAGMENT, name, std::nullopt,
+                                                  __FILE__, __LINE__);
+    g_moe_defs->def(
+        "moe_wna16_marlin_gemm(Tensor! a, Tensor? c_or_none,"
+        "Tensor! b_q_weight, Tensor? b_bias_or_none,"
+        "Tensor! b_scales, Tensor? global_scale, Tensor? "
+        "b_zeros_or_none,"
+        "Tensor? g_idx_or_none, Tensor? perm_or_none, Tensor! workspace,"
+        "Tensor sorted_token_ids,"
+        "Tensor! expert_ids, Tensor! num_tokens_past_padded,"
+        "Tensor! topk_weights, int moe_block_size, int top_k, "
+        "bool mul_topk_weights, bool is_ep, int b_q_type_id,"
+        "int size_m, int size_n, int size_k,"
+        "bool is_full_k, bool use_atomic_add,"
+        "bool use_fp32_reduce, bool is_zp_float) -> Tensor");
+    g_moe_impls = std::make_unique<torch::Library>(torch::Library::IMPL, name,
+                                                   c10::DispatchKey::CUDA, __FILE__, __LINE__);
+    g_moe_impls->impl("moe_wna16_marlin_gemm", &moe_wna16_marlin_gemm);
+  } catch (const std::exception&) {
+    g_moe_impls.reset();
+    g_moe_defs.reset();
     return -1;
   }
   return 0;
