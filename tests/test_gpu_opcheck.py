@@ -2,6 +2,7 @@
 autograd registration consistency), as the reference does for each of its ops
 (tests/kernels/utils.py:1300 `opcheck`, used at tests/kernels/quantization/
 test_marlin_gemm.py:141,196,310,419 and tests/kernels/core/test_permute_cols.py)."""
+import numpy as np
 import pytest
 
 from tests import helpers as H
