@@ -300,6 +300,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
       int st_i = 0;
       uint32_t st_ph = 0;
       bool ok = true;
+      // A comes from the kernel before this one in the stream (programmatic dependent launch:
+      // this kernel's launch and set-up overlap that kernel's tail)
+      asm volatile("griddepcontrol.wait;\n" ::: "memory");
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         const int t = item / KS, ks = item - t * KS;
         const int kb0 = (int)((long long)kb_total * ks / KS);
@@ -570,6 +573,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant_
       dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
     };
+    // C and the partial sums may still be read by the kernel before this one
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++tile_i) {
       const int t = item / KS;
       const int tn = t / m_tiles, tm = t % m_tiles;
@@ -720,7 +725,22 @@ static int launch_one(const CUtensorMap& map, const TcParams& p, cudaStream_t st
   const int items = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN) * p.ksplit;
   const int sms = device_sm_count();
   const int grid = items < sms ? items : sms;
-  kernel<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(map, b_map, p);
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // early launch only where this kernel's fixed costs matter: with many rows the waiting CTAs
+    // would take the SMs from an act-order gather still running in front (measured: down-proj
+    // M = 1024 129 -> 142 us)
+    cfg.numAttrs = (pdl_enabled() && p.m <= 128) ? 1 : 0;
+    B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, map, b_map, p));
+  }
   note_launch();
   B200Q_CUDA_OK(cudaGetLastError());
   if (p.ksplit > 1) {
