@@ -252,6 +252,8 @@ def run_ours(args, world, rank, local_rank):
     flags = _lib.FLAG_K_FULL | _lib.FLAG_FP32_REDUCE
     qtype = scalar_types.uint4b8
 
+    ar_side = torch.cuda.Stream(device=dev) if dist is not None else None
+
     def raw_call(p, m, copy, reduce=True):
         """One GEMM through the C ABI on the current stream, inputs resident in HBM.
         reduce=False leaves the row-parallel output un-reduced (GEMM-only timing)."""
@@ -263,6 +265,26 @@ def run_ours(args, world, rank, local_rank):
                 vp(p.perm.data_ptr()) if p.act_order else None, None, vp(c.data_ptr()),
                 vp(scratch.data_ptr()), max_scratch, vp(ws.data_ptr()), ws.numel(), qtype.id,
                 _lib.BF16, m, p.n, p.k, p.k // GROUP, flags)
+        if (reduce and not fused and dist is not None and p.row_parallel
+                and m >= D.OVERLAP_MIN_ROWS):
+            # what RowParallelLinear does with many rows: blocks of rows, NCCL's all-reduce of a
+            # block on a second stream beside the GEMM of the next block
+            step = -(-m // D.OVERLAP_CHUNKS)
+            cur_s = torch.cuda.current_stream()
+            for r0 in range(0, m, step):
+                rows = min(step, m - r0)
+                blk = list(args)
+                blk[0] = vp(a.data_ptr() + r0 * p.k * 2)
+                blk[8] = vp(c.data_ptr() + r0 * p.n * 2)
+                blk[15] = rows
+                _lib.check(lib.b200q_marlin_gemm(*blk, vp(cur_s.cuda_stream)), "b200q_marlin_gemm")
+                done = torch.cuda.Event()
+                done.record(cur_s)
+                with torch.cuda.stream(ar_side):
+                    ar_side.wait_event(done)
+                    dist.all_reduce(c[r0:r0 + rows])
+            cur_s.wait_stream(ar_side)
+            return
         cur = vp(torch.cuda.current_stream().cuda_stream)
         if fused:
             # GEMM and all-reduce in one call: one kernel at M <= 32, GEMM + peer-memory

@@ -90,6 +90,22 @@ def _worker(rank, world, port, q):
         want = D.tensor_model_parallel_all_reduce(part)
         got = layer(shard[:m].contiguous())
         ok &= bool(torch.equal(got, want))
+    # many rows: blocks of rows with NCCL's all-reduce beside the next block's GEMM give the bits of
+    # GEMM followed by one all-reduce, eagerly and under graph replay
+    big = torch.randn((1280, K // world), device=dev, generator=gen).to(torch.bfloat16)
+    want_big = D.tensor_model_parallel_all_reduce(layer.quant_method.apply(layer, big, None))
+    D.OVERLAP_MIN_ROWS = 1024               # (the default threshold is 8192 rows)
+    got_big = layer(big)
+    torch.cuda.synchronize()
+    ok &= got_big.shape == want_big.shape and bool(torch.equal(got_big, want_big))
+    g3 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g3):
+        o3 = layer(big)
+    for _ in range(3):
+        g3.replay()
+    torch.cuda.synchronize()
+    ok &= bool(torch.equal(o3, want_big))
+    del g3
     xs = shard[:16].contiguous()
     want = D.tensor_model_parallel_all_reduce(layer.quant_method.apply(layer, xs, None))
     side.wait_stream(torch.cuda.current_stream())

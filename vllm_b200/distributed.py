@@ -85,6 +85,40 @@ def tensor_model_parallel_all_reduce(input_: torch.Tensor) -> torch.Tensor:
     return out
 
 
+_OVERLAP_STREAMS: dict = {}
+# measured on 2 B200s: below 8192 rows the blocks are too short for NCCL's kernel to find free SMs
+# beside the persistent GEMM kernel (4096 rows, o-proj: 232 us plain, 254 us in two blocks, 380 us
+# in four), at 8192 rows four blocks win (down-proj of the 70B shard: 1719 -> 1594 us)
+OVERLAP_MIN_ROWS = 8192
+OVERLAP_CHUNKS = 4
+
+
+def overlapped_row_parallel(gemm, input_: torch.Tensor, chunks: int = OVERLAP_CHUNKS) -> torch.Tensor:
+    """Row-parallel GEMM over many rows with the collective hidden behind the compute: the rows are
+    cut into `chunks` blocks, block j's all-reduce (NCCL, on a second stream) runs while block
+    j + 1 is multiplied.  `gemm(x_block) -> partial output block`.  Works under CUDA-graph capture
+    (the second stream forks from and joins the capturing stream)."""
+    rows = input_.shape[0]
+    step = -(-rows // chunks)
+    cur = torch.cuda.current_stream(input_.device)
+    key = (input_.device.index, cur.cuda_stream)
+    side = _OVERLAP_STREAMS.get(key)
+    if side is None:
+        side = _OVERLAP_STREAMS[key] = torch.cuda.Stream(device=input_.device)
+    outs = []
+    for r0 in range(0, rows, step):
+        part = gemm(input_[r0:r0 + step])
+        done = torch.cuda.Event()
+        done.record(cur)
+        with torch.cuda.stream(side):
+            side.wait_event(done)
+            dist.all_reduce(part, op=dist.ReduceOp.SUM, group=_TP_GROUP)
+        part.record_stream(side)
+        outs.append(part)
+    cur.wait_stream(side)
+    return torch.cat(outs, dim=0) if len(outs) > 1 else outs[0]
+
+
 def tensor_model_parallel_all_gather(input_: torch.Tensor, dim: int = -1) -> torch.Tensor:
     if _TP_SIZE == 1:
         return input_

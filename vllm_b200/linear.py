@@ -10,6 +10,8 @@ are sharded in checkpoint format and each shard is repacked on its own rank.
 from __future__ import annotations
 
 import torch
+
+from . import distributed as D
 import torch.nn.functional as F
 
 from .distributed import (divide, reduce_link, get_tensor_model_parallel_rank,
@@ -181,4 +183,7 @@ class RowParallelLinear(LinearBase):
         if (link is not None and getattr(self.quant_method, "supports_reduce_link", False)
                 and link.fits(rows, self.output_size_per_partition, input_.dtype)):
             return self.quant_method.apply(self, input_, bias, reduce_link=link)
+        if input_.dim() == 2 and rows >= D.OVERLAP_MIN_ROWS and input_.is_cuda:
+            # many rows: NCCL's all-reduce of one block of rows runs beside the GEMM of the next
+            return D.overlapped_row_parallel(lambda x: self.quant_method.apply(self, x, bias), input_)
         return all_reduce(self.quant_method.apply(self, input_, bias))
