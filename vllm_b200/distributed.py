@@ -88,7 +88,8 @@ def tensor_model_parallel_all_reduce(input_: torch.Tensor) -> torch.Tensor:
 _OVERLAP_STREAMS: dict = {}
 # measured on 2 B200s: below 8192 rows the blocks are too short for NCCL's kernel to find free SMs
 # beside the persistent GEMM kernel (4096 rows, o-proj: 232 us plain, 254 us in two blocks, 380 us
-# in four), at 8192 rows four blocks win (down-proj of the 70B shard: 1719 -> 1594 us)
+# in four), at 8192 rows four blocks win (down-proj of the 70B shard, alternating runs on one box: 1681 / 1734 us
+# plain, 1576 / 1635 us in four blocks, 1755 us in two)
 OVERLAP_MIN_ROWS = 8192
 OVERLAP_CHUNKS = 4
 
