@@ -180,7 +180,10 @@ struct StreamCfg {
   static constexpr int kEpt = 2 * NTW;  // output elements per thread per 8-row block
 };
 
-template <typename T, int BITS, bool HAS_ZP, int GM, int MT, int NTW, int MINB>
+// MOE: the mixture-of-experts form (see gemm_lookup.cuh): blockIdx.y is a block of p.m sorted
+// ids, the rows of A come through the ids (row = id / top_k), the block's expert selects the
+// weights, output rows are the ids themselves.
+template <typename T, int BITS, bool HAS_ZP, int GM, int MT, int NTW, int MINB, bool MOE = false>
 __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const StreamParams p) {
   using Cfg = StreamCfg<BITS, HAS_ZP, GM, MT, NTW>;
   using E = Emb<T, BITS>;
@@ -198,6 +201,21 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
   const int NT = p.n / 64;
   const uint16_t* __restrict__ S = static_cast<const uint16_t*>(p.scales);
   const uint32_t ex = p.c_ex, mlo = p.c_mask_lo, mhi = p.c_mask_hi;
+  const unsigned char* __restrict__ Bw = reinterpret_cast<const unsigned char*>(p.b);
+  const uint32_t* __restrict__ Zp = p.zeros;
+  const uint16_t* __restrict__ Bias = static_cast<const uint16_t*>(p.bias);
+  const int32_t* moe_ids = nullptr;   // this block's sorted ids
+  if constexpr (MOE) {
+    // (uniform over the cluster: its CTAs share blockIdx.y)
+    if ((int)blockIdx.y * p.m >= *p.moe_num_padded) return;
+    const int expert = p.moe_expert_ids[blockIdx.y];
+    if (expert < 0) return;
+    moe_ids = p.moe_sorted_ids + (size_t)blockIdx.y * p.m;
+    Bw += (size_t)expert * p.moe_b_stride * 4;
+    S += (size_t)expert * p.moe_s_stride;
+    if (HAS_ZP) Zp += (size_t)expert * p.moe_z_stride;
+    if (p.bias) Bias += (size_t)expert * p.moe_bias_stride;
+  }
 
   // cluster = the CTAs that share one column slice; rank = which part of K
   uint32_t ksplit, krank;
@@ -225,8 +243,17 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
   constexpr int kABlocks = (MT + 1) / 2;                    // 16-row blocks of A
   const size_t a_blk_stride = (size_t)16 * p.lda * 2;
   int a_bytes[kABlocks];
+  long long a_row[kABlocks];  // source row of A this lane stages for each 16-row block
 #pragma unroll
-  for (int i = 0; i < kABlocks; ++i) a_bytes[i] = (i * 16 + fr < p.m) ? 16 : 0;
+  for (int i = 0; i < kABlocks; ++i) {
+    a_bytes[i] = (i * 16 + fr < p.m) ? 16 : 0;
+    a_row[i] = i * 16 + fr;
+    if constexpr (MOE) {
+      const int id = a_bytes[i] ? moe_ids[i * 16 + fr] : p.moe_rows;
+      a_bytes[i] = id < p.moe_rows ? 16 : 0;
+      a_row[i] = id / p.moe_top_k;
+    }
+  }
 
   // let the next kernel in the stream start its own weight prefetch early
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
@@ -264,10 +291,17 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
     }
 
     // ---- producer state -------------------------------------------------------------
-    const unsigned char* i_w = reinterpret_cast<const unsigned char*>(p.b) +
-                               ((size_t)wb * NT + nt0) * Cfg::kTileBytes + lane * 16;
+    const unsigned char* i_w = Bw + ((size_t)wb * NT + nt0) * Cfg::kTileBytes + lane * 16;
+    // running address of block 0's row; the other blocks at a constant distance from it
     const unsigned char* i_a = static_cast<const unsigned char*>(p.a) +
-                               ((size_t)(a_bytes[0] ? fr : 0) * p.lda + (size_t)wb * 16 + fh * 8) * 2;
+                               ((size_t)(a_bytes[0] ? a_row[0] : 0) * p.lda + (size_t)wb * 16 + fh * 8) * 2;
+    long long a_delta[MOE ? kABlocks : 1];  // moe: the rows of a block are wherever the ids say
+    (void)a_delta;
+    if constexpr (MOE) {
+#pragma unroll
+      for (int i = 0; i < kABlocks; ++i)
+        a_delta[i] = a_bytes[i] ? (a_row[i] - (a_bytes[0] ? a_row[0] : 0)) * (long long)p.lda * 2 : 0;
+    }
     uint32_t i_st = ring;  // next stage to fill
     const uint32_t ring_end = ring + D * Cfg::kStageBytes;
     const int gb = p.group_blocks;
@@ -301,8 +335,12 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
     auto issue_a = [&]() {
 #pragma unroll
       for (int i = 0; i < kABlocks; ++i)
-        cp_async16(i_st + Cfg::kAOff + i * 512 + a_fill_off,
-                   a_bytes[i] ? i_a + i * a_blk_stride : i_a, a_bytes[i]);
+        if constexpr (MOE)
+          cp_async16(i_st + Cfg::kAOff + i * 512 + a_fill_off, a_bytes[i] ? i_a + a_delta[i] : i_a,
+                     a_bytes[i]);
+        else
+          cp_async16(i_st + Cfg::kAOff + i * 512 + a_fill_off,
+                     a_bytes[i] ? i_a + i * a_blk_stride : i_a, a_bytes[i]);
       if (GM == kGrouped) {
         if (i_left == 0) {
           const uint32_t slot = slots + (i_g & (Cfg::kSlots - 1)) * Cfg::kSlotBytes;
@@ -313,7 +351,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
             constexpr int kChunks = NTW * 8 * BITS / 16;  // 16 B chunks of zero-point words
             const int zl = lane & (kChunks - 1);
             cp_async16(slot + Cfg::kSlotZOff + zl * 16,
-                       p.zeros + (size_t)i_g * (p.n * BITS / 32) + nt0 * (2 * BITS) + zl * 4);
+                       Zp + (size_t)i_g * (p.n * BITS / 32) + nt0 * (2 * BITS) + zl * 4);
           }
           ++i_g;
           i_left = i_first_left;
@@ -504,7 +542,7 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
           uint32_t zw[2];
           (void)zw;
           if (HAS_ZP) {
-            const uint32_t* zrow = p.zeros + (size_t)(nt0 + j) * (2 * BITS);
+            const uint32_t* zrow = Zp + (size_t)(nt0 + j) * (2 * BITS);
             if (BITS == 4) {
               zw[0] = __ldg(zrow + c8);
             } else {
@@ -640,16 +678,21 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
 #pragma unroll
       for (int e = 0; e < Cfg::kEpt; ++e) {
         cs[e] = (GM == kChannel) ? Pair<T>::to_float(S[single_perm_pos(n_base + e)]) : 1.f;
-        bs[e] = p.bias ? Pair<T>::to_float(
-                             static_cast<const uint16_t*>(p.bias)[single_perm_pos(n_base + e)])
-                       : 0.f;
+        bs[e] = p.bias ? Pair<T>::to_float(Bias[single_perm_pos(n_base + e)]) : 0.f;
       }
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
+        float tw = 1.f;
+        if constexpr (MOE) {
+          if (p.moe_topk_weights && i * 8 + o_row < p.m) {
+            const int id = moe_ids[i * 8 + o_row];
+            if (id < p.moe_rows) tw = p.moe_topk_weights[id];
+          }
+        }
 #pragma unroll
         for (int e = 0; e < Cfg::kEpt; e += 2) {
-          const float v0 = outv[i][e] * cs[e] + bs[e];
-          const float v1 = outv[i][e + 1] * cs[e + 1] + bs[e + 1];
+          const float v0 = (outv[i][e] * cs[e] + bs[e]) * tw;
+          const float v1 = (outv[i][e + 1] * cs[e + 1] + bs[e + 1]) * tw;
           packed[i][e / 2] =
               (uint32_t)Pair<T>::from_float(v0) | ((uint32_t)Pair<T>::from_float(v1) << 16);
         }
@@ -662,7 +705,12 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         if (!blk_mine(i)) continue;
-        uint16_t* dst = static_cast<uint16_t*>(p.c) + (size_t)(i * 8 + o_row) * p.n + n_base;
+        long long out_row = i * 8 + o_row;
+        if constexpr (MOE) {
+          out_row = moe_ids[i * 8 + o_row];      // output row = the sorted id; padding writes nothing
+          if (out_row >= p.moe_rows) continue;
+        }
+        uint16_t* dst = static_cast<uint16_t*>(p.c) + (size_t)out_row * p.n + n_base;
         if constexpr (Cfg::kEpt == 4)
           *reinterpret_cast<uint2*>(dst) = make_uint2(packed[i][0], packed[i][1]);
         else
@@ -728,14 +776,14 @@ __global__ void __launch_bounds__(kStreamThreads, MINB) gemm_stream_kernel(const
 }
 
 // Host launcher for one (type, bits, zp, group mode, MT, NTW) variant.
-template <typename T, int BITS, bool HAS_ZP, int GM, int MT, int NTW>
+template <typename T, int BITS, bool HAS_ZP, int GM, int MT, int NTW, bool MOE = false>
 int launch_stream(StreamParams p, int max_ctas, cudaStream_t stream) {
   using Cfg = StreamCfg<BITS, HAS_ZP, GM, MT, NTW>;
   using E = Emb<T, BITS>;
   // accumulator registers: acc (+ grp when grouped)
   constexpr int kAccRegs = MT * NTW * 16 * (GM == kGrouped ? 2 : 1);
   constexpr int kMinBlocks = (kAccRegs <= 64 && MT <= 2 && Cfg::kSmemBytes <= 112 * 1024) ? 2 : 1;
-  auto kernel = gemm_stream_kernel<T, BITS, HAS_ZP, GM, MT, NTW, kMinBlocks>;
+  auto kernel = gemm_stream_kernel<T, BITS, HAS_ZP, GM, MT, NTW, kMinBlocks, MOE>;
   static bool attr_done[64] = {};  // per device; benign race: the call is idempotent
   int dev = 0;
   B200Q_CUDA_OK(cudaGetDevice(&dev));
@@ -751,13 +799,14 @@ int launch_stream(StreamParams p, int max_ctas, cudaStream_t stream) {
   // least 8 k-tiles (one per warp) each
   const int target = device_sm_count() * kMinBlocks;
   int ksplit = 1;
-  while (ksplit < 8 && p.slices * ksplit * 2 <= target && p.kt_total / (ksplit * 2) >= 8) ksplit *= 2;
+  const int blocks = MOE ? p.moe_blocks : 1;
+  while (ksplit < 8 && p.slices * blocks * ksplit * 2 <= target && p.kt_total / (ksplit * 2) >= 8) ksplit *= 2;
   (void)max_ctas;
   const int grid = p.slices * ksplit;
   // programmatic dependent launch: the kernel may start while its predecessor in
   // the stream drains; it orders itself with griddepcontrol.wait
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = dim3(grid, blocks);
   cfg.blockDim = dim3(kStreamThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;

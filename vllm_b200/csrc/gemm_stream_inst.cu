@@ -105,6 +105,12 @@ int fp4_weights(const StreamParams& p, int gm, int rows8, int ntw, int max_ctas,
 // mixture-of-experts form: the reference-order kernel over (block of sorted ids, column slice)
 template <bool HAS_ZP, int GM>
 int moe_blocks(const StreamParams& p, int rows8, int max_ctas, cudaStream_t stream) {
+  // blocks of up to 32 ids: the decode kernel; above: the reference-order kernel
+  switch (rows8) {
+    case 1: return launch_stream<T, B, HAS_ZP, GM, 1, 1, true>(p, max_ctas, stream);
+    case 2: return launch_stream<T, B, HAS_ZP, GM, 2, 1, true>(p, max_ctas, stream);
+    case 4: return launch_stream<T, B, HAS_ZP, GM, 4, 1, true>(p, max_ctas, stream);
+  }
   const int mb = (rows8 + 1) / 2;  // 16-row blocks
   switch (mb) {
     case 1: return launch_lookup<T, B, HAS_ZP, GM, 1, 1, false, false, false, true>(p, max_ctas, stream);

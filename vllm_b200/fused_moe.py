@@ -60,7 +60,10 @@ def fused_marlin_moe(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Te
     N = w2.size(1) * 16
     assert w1.size(2) // 16 * pf == 2 * N and w2.size(2) // 16 * pf == K
     assert topk_weights.dtype == torch.float32
-    for block_size_m in (8, 16, 32, 48, 64):
+    # the reference walks 8, 16, 32, 48, 64 (fused_marlin_moe.py:286-288); here blocks of up to 32
+    # ids run the decode kernel, which is faster than the 48 / 64 path even when an expert's
+    # weights are then read twice
+    for block_size_m in (8, 16, 32):
         if M * topk / E / block_size_m < 0.9:
             break
     if global_num_experts == -1:
